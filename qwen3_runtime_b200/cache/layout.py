@@ -7,7 +7,7 @@ paged group has one page pool and one block table per request for all its
 layers, so one page id addresses that page in every layer of the group
 (as in qwen3_runtime/kv/paged.py:63-72, where the only group is "all layers").
 
-Device layout of a paged group: ``[layers, 2 (K,V), pages + 1, kv_heads,
+Device layout of a paged key/value group: ``[layers, 2 (K,V), pages + 1, kv_heads,
 page_size, head_dim]`` -- per (page, head) a contiguous ``[page_size, head_dim]``
 tile, so one key/value tile of a head is a single contiguous read.  The extra
 last page is a scratch page that padded rows of a captured decode step write to.
@@ -24,6 +24,16 @@ from .manager import GroupSpec
 class KVLayerSpec:
     num_kv_heads: int
     head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class LatentLayerSpec:
+    """One row of ``width`` elements per token, shared by all heads (a compressed key/value
+    latent, possibly followed by a shared rotated key part), optionally only a window of rows.
+    Device layout of such a group: ``[layers, pages + 1, page_size, width]``."""
+
+    width: int
     window: int | None = None
 
 
@@ -52,7 +62,7 @@ class CacheLayout:
             buckets.setdefault(spec, []).append(cache_id)
         self.groups: list[GroupLayout] = []
         for spec, ids in buckets.items():
-            if isinstance(spec, KVLayerSpec):
+            if isinstance(spec, (KVLayerSpec, LatentLayerSpec)):
                 gs = GroupSpec("window", spec.window) if spec.window else GroupSpec("full")
             elif isinstance(spec, StateLayerSpec):
                 gs = GroupSpec("state")
@@ -77,8 +87,11 @@ class CacheLayout:
         out = []
         for gi in self.paged_groups:
             g = self.groups[gi]
-            s: KVLayerSpec = g.layer_spec
-            out.append(len(g.cache_ids) * 2 * s.num_kv_heads * s.head_dim * page_size * dtype_bytes)
+            s = g.layer_spec
+            if isinstance(s, LatentLayerSpec):
+                out.append(len(g.cache_ids) * s.width * page_size * dtype_bytes)
+            else:
+                out.append(len(g.cache_ids) * 2 * s.num_kv_heads * s.head_dim * page_size * dtype_bytes)
         return out
 
     def token_bytes(self, dtype_bytes: int) -> int:

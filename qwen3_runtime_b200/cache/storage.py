@@ -6,7 +6,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .layout import CacheLayout, KVLayerSpec, StateLayerSpec
+from .layout import CacheLayout, KVLayerSpec, LatentLayerSpec, StateLayerSpec
 
 
 @dataclass
@@ -21,6 +21,7 @@ class CacheLayerView:
     v_pages: torch.Tensor | None
     state: torch.Tensor | None  # [slots + 1, *shape]
     writes: bool = True
+    latent_pages: torch.Tensor | None = None  # [pages + 1, page_size, width] (a latent group)
 
 
 class CacheStorage:
@@ -45,6 +46,10 @@ class CacheStorage:
                 pages = self.num_pages[layout.paged_groups.index(gi)]
                 shape = (len(g.cache_ids), 2, pages + 1, s.num_kv_heads, page_size, s.head_dim)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
+            elif isinstance(s, LatentLayerSpec):
+                pages = self.num_pages[layout.paged_groups.index(gi)]
+                shape = (len(g.cache_ids), pages + 1, page_size, s.width)
+                self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
             else:
                 assert isinstance(s, StateLayerSpec)
                 shape = (len(g.cache_ids), num_slots + 1, *s.shape)
@@ -56,6 +61,9 @@ class CacheStorage:
         gi, li = self.layout.where[cache_id]
         g = self.layout.groups[gi]
         t = self.tensors[gi]
+        if g.spec.paged and isinstance(g.layer_spec, LatentLayerSpec):
+            return CacheLayerView(gi, self.layout.paged_groups.index(gi), self.page_size, g.spec.window,
+                                  None, None, None, writes, latent_pages=t[li])
         if g.spec.paged:
             return CacheLayerView(gi, self.layout.paged_groups.index(gi), self.page_size, g.spec.window,
                                   t[li, 0], t[li, 1], None, writes)
@@ -75,8 +83,11 @@ class CacheStorage:
 
     def poison_pages(self, paged_index: int, pages: list[int], value: float = float("nan")) -> None:
         """Overwrite pages (tests: a page that is used again must not leak old contents)."""
-        t = self.tensors[self.layout.paged_groups[paged_index]]
-        if pages:
+        gi = self.layout.paged_groups[paged_index]
+        t = self.tensors[gi]
+        if pages and isinstance(self.layout.groups[gi].layer_spec, LatentLayerSpec):
+            t[:, torch.tensor(pages, dtype=torch.long, device=t.device)] = value
+        elif pages:
             t[:, :, torch.tensor(pages, dtype=torch.long, device=t.device)] = value
 
     def nbytes(self) -> int:

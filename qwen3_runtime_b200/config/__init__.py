@@ -1,4 +1,5 @@
 from .engine_config import EngineConfig, canonical_dtype
+from .logesun_config import LogesunConfig
 from .model_config import ConfigError, Qwen3Config
 from .registry import (
     Architecture,
@@ -20,6 +21,7 @@ __all__ = [
     "ConfigError",
     "EngineConfig",
     "LayerRun",
+    "LogesunConfig",
     "ModelSpec",
     "PartSpec",
     "Qwen3Config",

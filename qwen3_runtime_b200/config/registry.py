@@ -71,9 +71,11 @@ def _ensure_builtin() -> None:
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:
-    """Pick the registered architecture named in ``raw['architectures']``."""
+    """Pick the registered architecture named in ``raw['architectures']`` (or ``raw['architecture']``)."""
     _ensure_builtin()
-    names = raw.get("architectures") or []
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):  # some designs name themselves with one string
+        names.append(raw["architecture"])
     for name in names:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]

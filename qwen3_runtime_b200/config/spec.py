@@ -35,12 +35,15 @@ class LayerRun:
     weights are shared).  ``cache`` is the id of the cache layer the mixer uses;
     two entries with the same ``cache`` share keys and values.  ``writes`` says
     whether this entry stores its own keys/values (or state) there or only reads
-    what an earlier entry stored.
+    what an earlier entry stored.  ``add_embedding``: the embedding output (the
+    residual stream as it was before the first entry) is added to the stream right
+    before this entry runs (a looped stack that is fed its input again).
     """
 
     block: int
     cache: int
     writes: bool = True
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

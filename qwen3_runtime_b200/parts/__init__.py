@@ -1,4 +1,4 @@
-from . import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, experts, feed_forward, latent_attention, norm, position  # noqa: F401  (register the built-in parts)
 from .base import (
     BuildContext,
     ParamSpec,

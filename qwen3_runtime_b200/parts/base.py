@@ -27,7 +27,9 @@ class ParamSpec:
     ``matrix``  -- operand of a matrix product or lookup table: the compute dtype;
     ``vector``  -- small per-channel parameter: float32 (a lossless copy of bfloat16
                    storage; a tensor stored in 32-bit stays 32-bit);
-    ``int``     -- integer table: int32.
+    ``int``     -- integer table: int32;
+    ``matrix_f32`` -- a matrix whose product is computed in float32 whatever the compute dtype
+                   (a router): float32.
     """
 
     shape: tuple[int, ...]
@@ -152,11 +154,20 @@ class ResidualStream:
     ``[parts, tokens, hidden]``: partial sums of the sublayer's last product over ranges of
     its inner dimension, which the norm adds in order (one kernel less waits for the sum).  A fresh stream holds an embedding lookup instead of
     values: the first norm gathers the rows, stores them as ``resid`` and normalises.
+
+    ``pending_norm`` ``(weight, eps)``: what is pending is RMS-normalised with this weight (in
+    float32) before it is added -- a block that norms a sublayer's output as well as its input
+    leaves it here, so that the output norm, the add and the next input norm are one kernel.
+    ``add_source``: the embedding rows are to be added to the sum once more (a looped stack that
+    is fed its input again); the next norm does it and clears the flag.
     """
 
     def __init__(self, num_tokens: int, hidden_size: int, *, ids: torch.Tensor, table: torch.Tensor):
         self.num_tokens = num_tokens
         self.hidden_size = hidden_size
+        self.source: tuple[torch.Tensor, torch.Tensor] = (ids, table)
         self.embed: tuple[torch.Tensor, torch.Tensor] | None = (ids, table)
         self.resid: torch.Tensor | None = None
         self.pending: torch.Tensor | None = None
+        self.pending_norm: tuple[torch.Tensor, float] | None = None
+        self.add_source = False

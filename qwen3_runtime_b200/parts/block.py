@@ -1,5 +1,7 @@
 """Arrangement of parts in a block.  ``pre_norm``: x += mixer(norm(x)); x += ff(norm(x))
-(qwen3_runtime/models/qwen3.py:159-187, where each add is fused with the next norm)."""
+(qwen3_runtime/models/qwen3.py:159-187, where each add is fused with the next norm).
+``sandwich_norm``: a norm before and after each sublayer, x += norm_b(mixer(norm(x))) and
+x += norm_b(ff(norm(x))), the feed-forward being optional."""
 
 from __future__ import annotations
 
@@ -58,4 +60,75 @@ class PreNormBlock(Part):
         stream.pending = self.feed_forward.forward(h, step)
 
 
+class SandwichNormBlock(Part):
+    """A norm on the input and on the output of each sublayer.  The output norms run no kernel of
+    their own: the block leaves the sublayer's output on the stream together with the output
+    norm's weight, and whichever norm reads the stream next (this block's second input norm, the
+    next block's first, the model's final norm) normalises it, adds it and normalises the sum in
+    one kernel.  ``feed_forward`` may be None: the block is its mixer alone."""
+
+    category = "block"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.mixer = build_part("mixer", spec["mixer"], ctx)
+        self.mixer_norm = build_part("norm", spec["mixer_norm"], ctx)
+        self.mixer_out_norm = build_part("norm", spec["mixer_out_norm"], ctx)
+        self.children = {
+            spec.get("mixer_prefix", "mixer."): self.mixer,
+            spec.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm,
+            spec.get("mixer_out_norm_prefix", "mixer_out_norm."): self.mixer_out_norm,
+        }
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_out_norm = None
+        if spec.get("feed_forward") is not None:
+            self.feed_forward = build_part("feed_forward", spec["feed_forward"], ctx)
+            self.feed_forward_norm = build_part("norm", spec["feed_forward_norm"], ctx)
+            self.feed_forward_out_norm = build_part("norm", spec["feed_forward_out_norm"], ctx)
+            self.children.update({
+                spec.get("feed_forward_prefix", "feed_forward."): self.feed_forward,
+                spec.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm,
+                spec.get("feed_forward_out_norm_prefix", "feed_forward_out_norm."): self.feed_forward_out_norm,
+            })
+        self.entry_norm = self.mixer_norm
+        # full name -> (part, the part's own name for it); prefixes may be prefixes of one another
+        self._owners = {prefix + name: (part, name) for prefix, part in self.children.items()
+                        for name in part.param_specs()}
+
+    def exit_to(self, norms) -> None:
+        """A sublayer's output is normalised before it is added, so it is never taken as partial sums."""
+
+    def param_specs(self):
+        return {full: part.param_specs()[name] for full, (part, name) in self._owners.items()}
+
+    def load(self, tensors):
+        per_part: dict[int, dict] = {}
+        for full, (part, name) in self._owners.items():
+            per_part.setdefault(id(part), {})[name] = tensors[full]
+        for part in self.children.values():
+            part.load(per_part.get(id(part), {}))
+
+    def kernel_groups(self):
+        return ["norm", *[g for part in self.children.values() for g in part.kernel_groups()]]
+
+    def step_choosers(self):
+        return {name: fn for part in self.children.values() for name, fn in part.step_choosers().items()}
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def position_limit(self):
+        limits = [n for n in (part.position_limit() for part in self.children.values()) if n is not None]
+        return min(limits) if limits else None
+
+    def forward(self, stream: ResidualStream, step: StepContext, cache) -> None:
+        h = self.mixer_norm.add_norm(stream)
+        stream.pending = self.mixer.forward(h, step, cache)
+        stream.pending_norm = self.mixer_out_norm.pending_scale()
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.add_norm(stream)
+            stream.pending = self.feed_forward.forward(h, step)
+            stream.pending_norm = self.feed_forward_out_norm.pending_scale()
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)

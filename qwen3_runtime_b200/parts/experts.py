@@ -1,0 +1,97 @@
+"""Routed feed-forward: many small gated layers, each token through a few of them.
+
+    z = W_router h (float32)      s = score(z)      chosen = the ``top`` largest s
+    out = sum over chosen e of expert_e(w_e * h)  (+ shared(h))      w_e = s_e
+
+The score is a sigmoid and the weights are the chosen scores as they are (``renormalize``
+divides them by their sum).  ``weight_on`` says what the weight multiplies: the expert's
+``"input"`` or its ``"output"``; the two differ because an expert is not linear.  An expert is
+the clamped gated layer
+
+    g = min(W_gate x, limit)   u = clamp(W_up x, -limit, limit)   y = g * sigmoid(alpha g) * (u + up_offset)
+    expert(x) = W_down y
+
+Tokens are grouped by expert on the device (no host round trip, so a step with experts can be
+captured), each expert's products run over its own tokens only, and the results are summed per
+token in float32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, ParamSpec, Part, StepContext, register_part
+
+
+class RoutedExperts(Part):
+    category = "feed_forward"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.hidden_size = int(spec["hidden_size"])
+        self.num_experts = int(spec["num_experts"])
+        self.top = int(spec["top"])
+        self.expert_size = int(spec["expert_size"])
+        self.limit = float(spec["limit"])
+        self.alpha = float(spec.get("alpha", 1.702))
+        self.up_offset = float(spec.get("up_offset", 1.0))
+        self.score = spec.get("score", "sigmoid")
+        self.renormalize = bool(spec.get("renormalize", False))
+        self.weight_on = spec.get("weight_on", "input")
+        self.shared_size = int(spec["shared_size"]) if spec.get("shared_size") else 0
+        self.shared_limit = float(spec.get("shared_limit") or self.limit)
+        if self.score != "sigmoid":
+            raise ValueError(f"routed_experts scores with a sigmoid, not {self.score!r}")
+        if self.weight_on not in ("input", "output"):
+            raise ValueError("weight_on is 'input' or 'output'")
+        if not 1 <= self.top <= self.num_experts:
+            raise ValueError("top must lie in 1..num_experts")
+        self.router = self.gate_up = self.down = self.shared_gate_up = self.shared_down = None
+
+    def param_specs(self):
+        E, F, W = self.num_experts, self.expert_size, self.hidden_size
+        specs = {}
+        for e in range(E):
+            specs[f"e{e}.gate"] = ParamSpec((F, W))
+            specs[f"e{e}.up"] = ParamSpec((F, W))
+            specs[f"e{e}.down"] = ParamSpec((W, F))
+        specs["router"] = ParamSpec((E, W), "matrix_f32")
+        if self.shared_size:
+            specs["shared.gate"] = ParamSpec((self.shared_size, W))
+            specs["shared.up"] = ParamSpec((self.shared_size, W))
+            specs["shared.down"] = ParamSpec((W, self.shared_size))
+        return specs
+
+    def load(self, tensors):
+        E = self.num_experts
+        # per expert: gate rows, then up rows
+        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                    for e in range(E)]).contiguous()
+        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
+        self.router = tensors["router"].contiguous()
+        if self.shared_size:
+            self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            self.shared_down = tensors["shared.down"].contiguous()
+
+    def kernel_groups(self):
+        groups = ["experts", "norm"]
+        if self.ctx.dtype == torch.float32:
+            groups.append("gemm_f32")
+        else:
+            groups += ["gemm_small_m", "gemm_stream"]
+        return groups
+
+    def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
+        ops = self.ops
+        chosen, weights = ops.route_top(h, self.router, self.top, renormalize=self.renormalize)
+        shared = None
+        if self.shared_size:
+            mid = torch.empty((h.shape[0], self.shared_size), dtype=h.dtype, device=h.device)
+            ops.clamped_glu(ops.linear(h, self.shared_gate_up), mid, limit=self.shared_limit, alpha=self.alpha,
+                            up_offset=self.up_offset)
+            shared = ops.linear(mid, self.shared_down)
+        return ops.routed_experts(h, chosen, weights, self.gate_up, self.down, limit=self.limit, alpha=self.alpha,
+                                  up_offset=self.up_offset, weight_on=self.weight_on, shared=shared)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -19,23 +19,30 @@ class GatedMLP(Part):
         if activation != "silu":
             raise ValueError(f"gated_mlp has a silu kernel only, not {activation!r}")
         self.down_bias = bool(spec.get("down_bias", False))
+        # the stored tensors' names (after the part's prefix), for checkpoints that call them otherwise
+        names = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight",
+                     down_bias="down_proj.bias")
+        names.update(spec.get("names") or {})
+        self.names = names
         self.gate_up_weight = self.down_weight = self.down_bias_vec = None
 
     def param_specs(self):
+        n = self.names
         specs = {
-            "gate_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
-            "up_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
-            "down_proj.weight": ParamSpec((self.hidden_size, self.intermediate_size)),
+            n["gate"]: ParamSpec((self.intermediate_size, self.hidden_size)),
+            n["up"]: ParamSpec((self.intermediate_size, self.hidden_size)),
+            n["down"]: ParamSpec((self.hidden_size, self.intermediate_size)),
         }
         if self.down_bias:
-            specs["down_proj.bias"] = ParamSpec((self.hidden_size,), "vector")
+            specs[n["down_bias"]] = ParamSpec((self.hidden_size,), "vector")
         return specs
 
     def load(self, tensors):
         # one product for gate and up: gate rows first (utils/loader.py:51-53)
-        self.gate_up_weight = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.down_weight = tensors["down_proj.weight"].contiguous()
-        self.down_bias_vec = tensors.get("down_proj.bias")
+        n = self.names
+        self.gate_up_weight = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
+        self.down_weight = tensors[n["down"]].contiguous()
+        self.down_bias_vec = tensors.get(n["down_bias"])
 
     def kernel_groups(self):
         if self.ctx.dtype == torch.float32:

@@ -108,6 +108,8 @@ class DecoderModel:
         s = self.spec
         stream = ResidualStream(step.num_tokens, s.hidden_size, ids=step.token_ids, table=self.embed)
         for run in s.order:
+            if run.add_embedding:
+                stream.add_source = True
             self.blocks[run.block].forward(stream, step, storage.view(run.cache, run.writes))
         if step.num_logit_rows == 0:
             return None

@@ -16,13 +16,19 @@ class RMSNorm(Part):
         super().__init__(spec, ctx)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        # the stored tensor's name after the part's prefix ("" when the prefix is the whole name)
+        self.weight_name = str(spec.get("weight_name", "weight"))
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.size,), "vector")}
+        return {self.weight_name: ParamSpec((self.size,), "vector")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+
+    def pending_scale(self) -> tuple[torch.Tensor, float]:
+        """This norm as something the next norm applies to what is pending (``ResidualStream.pending_norm``)."""
+        return self.weight, self.eps
 
     def kernel_groups(self):
         return ["norm"]
@@ -36,6 +42,13 @@ class RMSNorm(Part):
         n = stream.num_tokens if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=self.ctx.device)
         keep = rows is None
+        extra = {}
+        if stream.pending is not None and stream.pending_norm is not None:
+            extra.update(post_weight=stream.pending_norm[0], post_eps=stream.pending_norm[1])
+        if stream.add_source:
+            if stream.embed is not None:
+                raise ValueError("the embedding cannot be added again before it was read once")
+            extra.update(add_ids=stream.source[0], add_table=stream.source[1])
         if stream.embed is not None:
             ids, table = stream.embed
             if keep:
@@ -43,14 +56,16 @@ class RMSNorm(Part):
                                            device=self.ctx.device)
             self.ops.fused_norm(out, self.weight, self.eps, resid=stream.resid if keep else None,
                                 pending=stream.pending, ids=ids, table=table, rows=rows, write_resid=keep,
-                                num_rows=n)
+                                num_rows=n, **extra)
             if keep:
                 stream.embed = None
         else:
             self.ops.fused_norm(out, self.weight, self.eps, resid=stream.resid, pending=stream.pending,
-                                rows=rows, write_resid=keep, num_rows=n)
+                                rows=rows, write_resid=keep, num_rows=n, **extra)
         if keep:
             stream.pending = None
+            stream.pending_norm = None
+            stream.add_source = False
         return out
 
 

@@ -64,5 +64,47 @@ class RotaryNeox(Part):
         return self.ctx.shared[key]
 
 
+class RotaryInterleaved(Part):
+    """Pairs (2i, 2i + 1) of the first ``rotary_dim`` elements turn by ``p * theta^(-2i / rotary_dim)``.
+    It keeps no table: the kernels that apply it work the angle out in float32 from the position and
+    :meth:`inverse_frequencies`, so no position is out of reach.  (With ``max_positions`` it also
+    offers tables, for mixers whose q/k kernel reads them.)"""
+
+    category = "position"
+    style = "rotary"
+    pairing = "interleaved"
+
+    def __init__(self, spec, ctx: BuildContext):
+        super().__init__(spec, ctx)
+        self.rotary_dim = int(spec["rotary_dim"])
+        self.theta = float(spec["theta"])
+        self.max_positions = spec.get("max_positions")
+        if self.rotary_dim < 2 or self.rotary_dim % 2:
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be a positive even number")
+
+    def kernel_groups(self):
+        return ["rope_kv"] if self.max_positions else []
+
+    def position_limit(self):
+        return int(self.max_positions) if self.max_positions else None
+
+    def inverse_frequencies(self) -> torch.Tensor:
+        """float32 ``[rotary_dim / 2]`` on the device, shared by the parts of one model."""
+        key = ("rope_interleaved_inv", self.rotary_dim, self.theta)
+        if key not in self.ctx.shared:
+            exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float) / self.rotary_dim
+            self.ctx.shared[key] = (1.0 / (self.theta ** exponents)).to(self.ctx.device)
+        return self.ctx.shared[key]
+
+    def rotation_tables(self):
+        if not self.max_positions:
+            raise ValueError("rope_interleaved without max_positions keeps no tables")
+        key = ("rope_interleaved", self.rotary_dim, self.theta, int(self.max_positions))
+        if key not in self.ctx.shared:
+            self.ctx.shared[key] = self.ops.rope_table(self.inverse_frequencies(), int(self.max_positions))
+        return self.ctx.shared[key]
+
+
 register_part("position", "none", NoPosition)
+register_part("position", "rope_interleaved", RotaryInterleaved)
 register_part("position", "rope_neox", RotaryNeox)

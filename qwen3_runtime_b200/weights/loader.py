@@ -111,7 +111,7 @@ def place(tensor: torch.Tensor, spec: ParamSpec, dtype: torch.dtype, device) -> 
         return tensor.to(device=device, dtype=torch.int32)
     if not tensor.is_floating_point():
         raise WeightError("a floating-point tensor is stored as integers")
-    if spec.kind == "vector":
+    if spec.kind in ("vector", "matrix_f32"):
         return tensor.to(device=device, dtype=torch.float32)
     return tensor.to(device=device, dtype=dtype)
 

@@ -20,7 +20,7 @@ class TorchOps:
 
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
-                   write_resid=True, num_rows=None):
+                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None):
         n = out.shape[0] if num_rows is None else num_rows
         src = rows[:n].long() if rows is not None else torch.arange(n, device=out.device)
         if ids is not None:
@@ -31,9 +31,14 @@ class TorchOps:
             total = pending[0][src]
             for p in range(1, pending.shape[0]):
                 total = total + pending[p][src]
-            v = v + total
         elif pending is not None:
-            v = v + pending[src].float()
+            total = pending[src].float()
+        if pending is not None:
+            if post_weight is not None:  # what is pending is normalised before it is added
+                total = (total * torch.rsqrt(total.pow(2).mean(-1, keepdim=True) + post_eps)) * post_weight.float()
+            v = v + total
+        if add_ids is not None:
+            v = v + add_table[add_ids.long()[src]].float()
         if write_resid:
             resid[src] = v
         var = v.pow(2).mean(-1, keepdim=True)
@@ -109,6 +114,96 @@ class TorchOps:
             probs = torch.softmax(scores, dim=-1)
             out[t] = torch.einsum("hn,nhd->hd", probs, vh).reshape(-1).to(out.dtype)
         return out
+
+    # ---- attention through a latent ------------------------------------------------------
+    @staticmethod
+    def _turn(x, pos, inv_freq):
+        """Interleaved pairs of the leading 2 * len(inv_freq) elements of the last axis; x [T, ..., n] float."""
+        if inv_freq is None:
+            return x
+        pairs = inv_freq.numel()
+        ang = pos.float()[:, None] * inv_freq.float()[None, :]
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [pairs]
+        c, s = ang.cos().reshape(shape), ang.sin().reshape(shape)
+        u, v = x[..., 0:2 * pairs:2], x[..., 1:2 * pairs:2]
+        out = x.clone()
+        out[..., 0:2 * pairs:2] = u * c - v * s
+        out[..., 1:2 * pairs:2] = v * c + u * s
+        return out
+
+    def latent_norm_rope_store(self, down, *, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, inv_freq, positions,
+                               token_seq, block_table, pages, page_size, write, q_out):
+        x = down.float()
+        a = x[:, :q_rank]
+        q_out.copy_(((a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps)) * q_weight.float()).to(q_out.dtype))
+        if not write:
+            return
+        c = x[:, q_rank:q_rank + kv_rank]
+        c = (c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps)) * kv_weight.float()
+        k = self._turn(x[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim], positions.long(), inv_freq)
+        row = torch.cat([c, k], dim=-1).to(pages.dtype)
+        for t in range(down.shape[0]):
+            p = int(positions[t])
+            page = int(block_table[int(token_seq[t]), p // page_size])
+            pages[page, p % page_size] = row[t]
+
+    def head_linear(self, x, weight, out):
+        """out[t, h] = weight[h] @ x[t, h]; x [T, H, K], weight [H, N, K], out [T, H, N] (views allowed)."""
+        out.copy_(torch.einsum("thk,hnk->thn", x.float(), weight.float()).to(out.dtype))
+        return out
+
+    def rotate_heads(self, x, out, *, positions, inv_freq):
+        out.copy_(self._turn(x.float(), positions.long(), inv_freq).to(out.dtype))
+        return out
+
+    def latent_attention(self, q, *, pages, value_dim, block_table, token_seq, positions, sink, out, page_size, scale,
+                         window, step=None):
+        T = q.shape[0]
+        for t in range(T):
+            p = int(positions[t])
+            lo = max(0, p - window + 1) if window else 0
+            table = block_table[int(token_seq[t])]
+            js = torch.arange(lo, p + 1)
+            rows = pages[table[js // page_size].long(), js % page_size].float()  # [n, width]
+            scores = (q[t].float() @ rows.t()) * scale  # [H, n]
+            if sink is not None:
+                scores = torch.cat([scores, sink.float()[:, None]], dim=-1)
+            probs = torch.softmax(scores, dim=-1)[:, : js.numel()]
+            out[t] = (probs @ rows[:, :value_dim]).to(out.dtype)
+        return out
+
+    # ---- routed experts ----------------------------------------------------------------
+    def route_top(self, h, router, top, renormalize=False):
+        scores = torch.sigmoid(h.float() @ router.float().t())
+        best = torch.topk(scores, top, dim=-1)
+        w = best.values
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        return best.indices.to(torch.int32), w.float()
+
+    def clamped_glu(self, gate_up, out, *, limit, alpha, up_offset):
+        F = out.shape[-1]
+        g = gate_up[:, :F].float().clamp(max=limit)
+        u = gate_up[:, F:].float().clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(alpha * g) * (u + up_offset)).to(out.dtype))
+        return out
+
+    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit, alpha, up_offset, weight_on="input",
+                       shared=None):
+        T, W = h.shape
+        F = gate_up.shape[1] // 2
+        total = torch.zeros((T, W), dtype=torch.float32, device=h.device)
+        for t in range(T):
+            for e, w in zip(chosen[t].tolist(), weights[t].tolist()):
+                x = (h[t].float() * w).to(h.dtype) if weight_on == "input" else h[t]
+                gu = (gate_up[e].float() @ x.float()).to(h.dtype)
+                mid = torch.empty((1, F), dtype=h.dtype, device=h.device)
+                self.clamped_glu(gu[None], mid, limit=limit, alpha=alpha, up_offset=up_offset)
+                y = (down[e].float() @ mid[0].float()).to(h.dtype).float()
+                total[t] += y if weight_on == "input" else y * w
+        if shared is not None:
+            total += shared.float()
+        return total.to(h.dtype)
 
     # ---- matrix products ----------------------------------------------------------------
     partial_parts = 0  # > 1: linear(partial_sums=True) answers with that many planes
