@@ -1,0 +1,362 @@
+// Routed experts: router scores and choice, grouping of (token, choice) slots by expert on the
+// device, the experts' two products over their own slots, and the per-token sum.
+//
+//   route_top      z = W_router h in fp32, s = sigmoid(z), the `top` largest s (lowest index on a
+//                  tie) with their scores as weights (optionally divided by their sum)
+//   group_slots    slots sorted by expert: offsets[E + 1], order[S], and for the products the
+//                  first row tile of each expert, tile_offsets[E + 1] (tiles of EXPERT_BM slots)
+//   expert_gate_up mid[slot] = glu(W_gate_e x, W_up_e x), x = h[token] * weight (rounded to the
+//                  operand type) when the weight multiplies the expert's input
+//                  glu: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + off)
+//   expert_down    y[slot] = W_down_e mid[slot]
+//   combine        out[t] = sum over the token's slots of y (times the weight when it multiplies
+//                  the output), plus the shared expert's result, summed in fp32 in slot order
+//
+// Products accumulate in fp32 on the FMA pipes, each output one accumulator over ascending k, so a
+// token's result does not depend on which other tokens chose the same expert.  Nothing here reads
+// a count back on the host: grids are sized for the worst case and surplus blocks leave at once.
+#include "common.cuh"
+
+constexpr int EXPERT_BM = 32;
+
+// ---- router ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void route_top_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ router, int E,
+                                 int W, int top, int renormalize, int* __restrict__ chosen,
+                                 float* __restrict__ weights) {
+  extern __shared__ float scores[];  // E
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const T* row = h + (long)t * h_stride;
+  for (int e = warp; e < E; e += nwarp) {
+    const float* wr = router + (long)e * W;
+    float dot = 0.f;
+    for (int i = lane; i < W; i += 32) dot = fmaf(to_f32(row[i]), wr[i], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) scores[e] = 1.f / (1.f + expf(-dot));
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float s = scores[e];
+      if (s > best) {
+        best = s;
+        at = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if (lane == 0) {
+      chosen[(long)t * top + k] = at;
+      weights[(long)t * top + k] = best;
+      scores[at] = -2.f;  // below every sigmoid
+    }
+    total += best;
+    __syncwarp();
+  }
+  if (renormalize)
+    for (int k = lane; k < top; k += 32) weights[(long)t * top + k] /= total;
+}
+
+Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float* router, int num_tokens, int E, int W,
+                           int top, int renormalize, int* chosen, float* weights, cudaStream_t stream) {
+  if (!h || !router || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
+  if (E > 8192) return Q3_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return Q3_OK;
+  const size_t smem = (size_t)E * sizeof(float);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(route_top_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (const float*)h, h_stride,
+                   router, E, W, top, renormalize, chosen, weights);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(route_top_kernel<bf16>, dim3(num_tokens), dim3(128), smem, stream, (const bf16*)h, h_stride, router,
+                   E, W, top, renormalize, chosen, weights);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- slots grouped by expert ----------------------------------------------------------------------
+// One block, for a few hundred slots.  Slots of one expert keep their order (slot s before slot
+// s' > s), so the grouping is the same on every run.
+__global__ void group_slots_kernel(const int* __restrict__ chosen, int S, int E, int* __restrict__ offsets,
+                                   int* __restrict__ tile_offsets, int* __restrict__ order) {
+  extern __shared__ int sm[];  // counts[E], cursor[E]
+  int* counts = sm;
+  int* cursor = sm + E;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int s = threadIdx.x; s < S; s += blockDim.x) atomicAdd(&counts[chosen[s]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      tile_offsets[e] = tiles;
+      cursor[e] = at;
+      at += counts[e];
+      tiles += (counts[e] + EXPERT_BM - 1) / EXPERT_BM;
+    }
+    offsets[E] = at;
+    tile_offsets[E] = tiles;
+  }
+  __syncthreads();
+  // a slot's place in its expert's group is the number of earlier slots with the same expert
+  for (int s = threadIdx.x; s < S; s += blockDim.x) {
+    const int e = chosen[s];
+    int rank = 0;
+    for (int r = 0; r < s; ++r) rank += chosen[r] == e;
+    order[cursor[e] + rank] = s;
+  }
+}
+
+// The same for many slots: placement by atomic cursor (the order inside an expert's group may then
+// differ from run to run; every slot's result is computed on its own, so the outputs do not).
+__global__ void group_slots_atomic_kernel(const int* __restrict__ chosen, int S, int E, int* __restrict__ offsets,
+                                          int* __restrict__ tile_offsets, int* __restrict__ order) {
+  extern __shared__ int sm[];
+  int* counts = sm;
+  int* cursor = sm + E;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int s = threadIdx.x; s < S; s += blockDim.x) atomicAdd(&counts[chosen[s]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      tile_offsets[e] = tiles;
+      cursor[e] = at;
+      at += counts[e];
+      tiles += (counts[e] + EXPERT_BM - 1) / EXPERT_BM;
+    }
+    offsets[E] = at;
+    tile_offsets[E] = tiles;
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < S; s += blockDim.x) order[atomicAdd(&cursor[chosen[s]], 1)] = s;
+}
+
+Q3_EXPORT int q3_group_slots(const int* chosen, int S, int E, int* offsets, int* tile_offsets, int* order,
+                             cudaStream_t stream) {
+  if (!chosen || !offsets || !tile_offsets || !order || E < 1 || S < 0) return Q3_ERR_ARGUMENT;
+  if (E > 8192) return Q3_ERR_UNSUPPORTED;
+  const size_t smem = 2 * (size_t)E * sizeof(int);
+  cudaError_t e;
+  if (S <= 512)
+    e = launch_pdl(group_slots_kernel, dim3(1), dim3(512), smem, stream, chosen, S, E, offsets, tile_offsets, order);
+  else
+    e = launch_pdl(group_slots_atomic_kernel, dim3(1), dim3(1024), smem, stream, chosen, S, E, offsets, tile_offsets,
+                   order);
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- the experts' products ------------------------------------------------------------------------
+__device__ __forceinline__ int expert_of_tile(const int* __restrict__ tile_offsets, int E, int tile) {
+  int lo = 0, hi = E;  // the last e with tile_offsets[e] <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_offsets[mid] <= tile) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// GATE_UP: A rows are h[token(slot)] (times the slot's weight when scale_input), B is the expert's
+// [2F, W] (gate rows, then up rows), the result mid[slot, F].  Else: A rows are mid[slot], B is the
+// expert's [W, F], the result y[slot, W].
+template <typename T, bool GATE_UP>
+__global__ void __launch_bounds__(256)
+expert_gemm_kernel(const T* __restrict__ A, long a_stride, const T* __restrict__ B, T* __restrict__ C, int N, int K,
+                   const int* __restrict__ offsets, const int* __restrict__ tile_offsets,
+                   const int* __restrict__ order, const float* __restrict__ weights, int E, int top,
+                   int scale_input, float limit, float alpha, float up_offset) {
+  constexpr int BM = EXPERT_BM, BN = 64, BK = 16, TM = 2, TN = 4, THREADS = 256;
+  constexpr int NB = GATE_UP ? 2 : 1;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[NB][BK][BN + 4];
+  __shared__ int slot_of[BM];
+  __shared__ float scale_of[BM];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tile = blockIdx.y;
+  if (tile >= tile_offsets[E]) return;
+  const int e = expert_of_tile(tile_offsets, E, tile);
+  const int row0 = offsets[e] + (tile - tile_offsets[e]) * BM;
+  const int rows = min(BM, offsets[e + 1] - row0);
+  const int tid = threadIdx.x;
+  if (tid < BM) {
+    const int slot = tid < rows ? order[row0 + tid] : -1;
+    slot_of[tid] = slot;
+    scale_of[tid] = (slot >= 0 && GATE_UP && scale_input) ? weights[slot] : 1.f;
+  }
+  __syncthreads();
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const int n0 = blockIdx.x * BN;
+  const T* Be = B + (long)e * (GATE_UP ? 2 : 1) * N * K;
+  float acc[NB][TM][TN];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[b][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int x = tid; x < BM * BK; x += THREADS) {
+      const int r = x / BK, c = x % BK;
+      const int slot = slot_of[r], gk = k0 + c;
+      float a = 0.f;
+      if (slot >= 0 && gk < K) {
+        const long arow = GATE_UP ? slot / top : slot;
+        a = to_f32(A[arow * a_stride + gk]);
+        if (GATE_UP && scale_input) a = to_f32(from_f32<T>(a * scale_of[r]));
+      }
+      As[c][r] = a;
+    }
+    for (int x = tid; x < NB * BN * BK; x += THREADS) {
+      const int b = x / (BN * BK), y = x % (BN * BK);
+      const int r = y / BK, c = y % BK;
+      const int gn = n0 + r, gk = k0 + c;
+      Ws[b][c][r] = (gn < N && gk < K) ? to_f32(Be[((long)b * N + gn) * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float w[TN];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) w[j] = Ws[b][kk][tx * TN + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[b][i][j] = fmaf(a[i], w[j], acc[b][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int slot = slot_of[ty * TM + i];
+    if (slot < 0) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int gn = n0 + tx * TN + j;
+      if (gn >= N) continue;
+      if (GATE_UP) {
+        // both products are rounded to the operand type before the gated unit, as two separate
+        // products followed by an activation kernel would
+        const float g = fminf(to_f32(from_f32<T>(acc[0][i][j])), limit);
+        const float u = fminf(fmaxf(to_f32(from_f32<T>(acc[NB - 1][i][j])), -limit), limit);
+        C[(long)slot * N + gn] = from_f32<T>((g / (1.f + expf(-alpha * g))) * (u + up_offset));
+      } else {
+        C[(long)slot * N + gn] = from_f32<T>(acc[0][i][j]);
+      }
+    }
+  }
+}
+
+// h: [T, W] rows h_stride apart; gate_up: [E, 2F, W]; mid: [S, F]; S = T * top slots.
+Q3_EXPORT int q3_expert_gate_up(int dtype, const void* h, long h_stride, const void* gate_up, void* mid, int S, int E,
+                                int F, int W, int top, const int* offsets, const int* tile_offsets, const int* order,
+                                const float* weights, int scale_input, float limit, float alpha, float up_offset,
+                                cudaStream_t stream) {
+  if (!h || !gate_up || !mid || !offsets || !tile_offsets || !order || !weights) return Q3_ERR_ARGUMENT;
+  if (E < 1 || F < 1 || W < 1 || top < 1) return Q3_ERR_ARGUMENT;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / EXPERT_BM + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((F + 63) / 64, tiles);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(expert_gemm_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)h, h_stride,
+                   (const float*)gate_up, (float*)mid, F, W, offsets, tile_offsets, order, weights, E, top, scale_input,
+                   limit, alpha, up_offset);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(expert_gemm_kernel<bf16, true>, grid, dim3(256), 0, stream, (const bf16*)h, h_stride,
+                   (const bf16*)gate_up, (bf16*)mid, F, W, offsets, tile_offsets, order, weights, E, top, scale_input,
+                   limit, alpha, up_offset);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// mid: [S, F]; down: [E, W, F]; y: [S, W].
+Q3_EXPORT int q3_expert_down(int dtype, const void* mid, const void* down, void* y, int S, int E, int F, int W,
+                             const int* offsets, const int* tile_offsets, const int* order, cudaStream_t stream) {
+  if (!mid || !down || !y || !offsets || !tile_offsets || !order || E < 1 || F < 1 || W < 1) return Q3_ERR_ARGUMENT;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / EXPERT_BM + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((W + 63) / 64, tiles);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(expert_gemm_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)mid, (long)F,
+                   (const float*)down, (float*)y, W, F, offsets, tile_offsets, order, (const float*)nullptr, E, 1, 0,
+                   0.f, 0.f, 0.f);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(expert_gemm_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16*)mid, (long)F,
+                   (const bf16*)down, (bf16*)y, W, F, offsets, tile_offsets, order, (const float*)nullptr, E, 1, 0, 0.f,
+                   0.f, 0.f);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- per-token sum ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
+                               T* __restrict__ out, long total, int W, int top) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / W;
+  const int i = (int)(idx - t * W);
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const float v = to_f32(y[(t * top + k) * W + i]);
+    sum += weights ? v * weights[t * top + k] : v;
+  }
+  if (shared) sum += to_f32(shared[idx]);
+  out[idx] = from_f32<T>(sum);
+}
+
+// y: [T * top, W]; weights: fp32 [T * top] or null (the weight was applied to the input);
+// shared: [T, W] or null; out: [T, W].
+Q3_EXPORT int q3_expert_combine(int dtype, const void* y, const float* weights, const void* shared, void* out,
+                                int num_tokens, int W, int top, cudaStream_t stream) {
+  if (!y || !out || W < 1 || top < 1) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_tokens * W;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)y, weights,
+                   (const float*)shared, (float*)out, total, W, top);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(combine_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)y, weights,
+                   (const bf16*)shared, (bf16*)out, total, W, top);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}

@@ -287,3 +287,130 @@ Q3_EXPORT int q3_logit_scale_cap(float* logits, long total, float scale, float c
   logit_scale_cap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(logits, total, scale, cap);
   return q3_launch_status();
 }
+
+// ---- RMSNorm of the sum, with what is pending normalised before it is added -----------------------
+// For blocks that norm a sublayer's output as well as its input:
+//   y   = pending[r]                                              (the sublayer's output, fp32 math)
+//   y'  = post_w ? (y * rsqrt(mean(y^2) + post_eps)) * post_w : y
+//   v   = (ids ? table[ids[r]] : resid[r]) + y' + (add_ids ? add_table[add_ids[r]] : 0)
+//   resid[r] = v (when write_resid);   out[i] = (v * rsqrt(mean(v^2) + eps)) * w
+// `add_ids/add_table` add embedding rows to the sum once more (a looped stack fed its input again).
+// One block per row; the row's y and v stay in shared memory between the passes.
+template <typename T>
+__global__ void fused_post_norm_kernel(const T* __restrict__ pending, const float* __restrict__ post_w, float post_eps,
+                                       float* __restrict__ resid, const int* __restrict__ ids,
+                                       const T* __restrict__ table, const int* __restrict__ add_ids,
+                                       const T* __restrict__ add_table, const int* __restrict__ rows,
+                                       const float* __restrict__ w, T* __restrict__ out, int H, float eps,
+                                       int write_resid, int vocab) {
+  extern __shared__ float vals[];  // y[H], v[H], 33 for the reductions
+  float* ys = vals;
+  float* vs = vals + H;
+  float* red = vals + 2 * H;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  float post_rstd = 1.f;
+  if (pending) {
+    const T* prow = pending + src * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float y = to_f32(prow[i]);
+      ys[i] = y;
+      ss += y * y;
+    }
+    if (post_w) post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+  }
+  const T* trow = nullptr;
+  if (ids) {
+    int id = ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    trow = table + (long)id * H;
+  }
+  const T* arow = nullptr;
+  if (add_ids) {
+    int id = add_ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    arow = add_table + (long)id * H;
+  }
+  float* rrow = resid ? resid + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = trow ? to_f32(trow[i]) : rrow[i];
+    if (pending) v += post_w ? (ys[i] * post_rstd) * post_w[i] : ys[i];
+    if (arow) v += to_f32(arow[i]);
+    if (write_resid) rrow[i] = v;
+    vs[i] = v;
+    ss += v * v;
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  T* orow = out + (long)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>((vs[i] * rstd) * w[i]);
+}
+
+template <typename T>
+static int launch_fused_post_norm(const void* pending, const float* post_w, float post_eps, float* resid,
+                                  const int* ids, const void* table, const int* add_ids, const void* add_table,
+                                  const int* rows, const float* w, void* out, int num_rows, int H, float eps,
+                                  int write_resid, int vocab, cudaStream_t stream) {
+  if (num_rows == 0) return Q3_OK;
+  const size_t smem = (size_t)(2 * H + 33) * sizeof(float);
+  if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(fused_post_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+  return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending, post_w,
+                    post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, rows, w, (T*)out, H, eps,
+                    write_resid, vocab) == cudaSuccess
+             ? Q3_OK
+             : Q3_ERR_LAUNCH;
+}
+
+// pending, table, add_table and out have `dtype`; post_w and w are fp32 [H]; resid is fp32.
+Q3_EXPORT int q3_fused_post_norm(int dtype, const void* pending, const float* post_w, float post_eps, float* resid,
+                                 const int* ids, const void* table, const int* add_ids, const void* add_table,
+                                 const int* rows, const float* w, void* out, int num_rows, int H, float eps,
+                                 int write_resid, int vocab, cudaStream_t stream) {
+  if (!w || !out || H < 1) return Q3_ERR_ARGUMENT;
+  if (!ids && !resid) return Q3_ERR_ARGUMENT;
+  if ((ids && !table) || (add_ids && !add_table)) return Q3_ERR_ARGUMENT;
+  if (write_resid && !resid) return Q3_ERR_ARGUMENT;
+  if (post_w && !pending) return Q3_ERR_ARGUMENT;
+  if (dtype == Q3_DTYPE_F32)
+    return launch_fused_post_norm<float>(pending, post_w, post_eps, resid, ids, table, add_ids, add_table, rows, w, out,
+                                         num_rows, H, eps, write_resid, vocab, stream);
+  if (dtype == Q3_DTYPE_BF16)
+    return launch_fused_post_norm<bf16>(pending, post_w, post_eps, resid, ids, table, add_ids, add_table, rows, w, out,
+                                        num_rows, H, eps, write_resid, vocab, stream);
+  return Q3_ERR_ARGUMENT;
+}
+
+// ---- clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit),
+//      out = g * sigmoid(alpha * g) * (u + up_offset); gu rows are [gate (F) | up (F)] ----
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int F, float limit,
+                                   float alpha, float up_offset) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / F;
+  const int i = (int)(idx - t * F);
+  const float g = fminf(to_f32(gu[t * 2 * F + i]), limit);
+  const float u = fminf(fmaxf(to_f32(gu[t * 2 * F + F + i]), -limit), limit);
+  out[idx] = from_f32<T>((g / (1.f + expf(-alpha * g))) * (u + up_offset));
+}
+
+Q3_EXPORT int q3_clamped_glu(int dtype, const void* gu, void* out, int num_rows, int F, float limit, float alpha,
+                             float up_offset, cudaStream_t stream) {
+  if (!gu || !out || F < 1) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * F;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == Q3_DTYPE_F32)
+    clamped_glu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, total, F, limit, alpha, up_offset);
+  else if (dtype == Q3_DTYPE_BF16)
+    clamped_glu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, total, F, limit, alpha, up_offset);
+  else
+    return Q3_ERR_ARGUMENT;
+  return q3_launch_status();
+}

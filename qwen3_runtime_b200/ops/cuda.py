@@ -55,6 +55,33 @@ _SIGNATURES = {
         "q3_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "q3_add_bias": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "q3_logit_scale_cap": [c_void_p, c_long, c_float, c_float, c_void_p],
+        "q3_fused_post_norm": [c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "q3_clamped_glu": [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    },
+    "latent_attention": {
+        "q3_latent_norm_rope_store": [c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                      c_int, c_void_p, c_void_p],
+        "q3_rotate_heads": [c_int, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_int, c_void_p],
+        "q3_latent_attention": [c_int, c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_float, c_int,
+                                c_void_p],
+    },
+    "head_gemm": {
+        "q3_head_linear": [c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int,
+                           c_int, c_void_p],
+    },
+    "experts": {
+        "q3_route_top": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                         c_void_p],
+        "q3_group_slots": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "q3_expert_gate_up": [c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p],
+        "q3_expert_down": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_void_p],
+        "q3_expert_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "rope_kv": {
         "q3_qk_norm_rope_store": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -242,13 +269,31 @@ class CudaOps:
 
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
-                   write_resid=True, num_rows=None):
+                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None):
         """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu.
         ``pending`` is ``[rows, H]`` of the output's type, or fp32 ``[parts, rows, H]``: the
-        partial sums of a product (:meth:`linear` with ``partial_sums``), added in order."""
+        partial sums of a product (:meth:`linear` with ``partial_sums``), added in order.
+        ``post_weight`` / ``post_eps``: what is pending is RMS-normalised with this weight before it
+        is added; ``add_ids`` / ``add_table``: embedding rows added to the sum as well."""
         H = weight.numel()
         n = out.shape[0] if num_rows is None else num_rows
         vocab = table.shape[0] if table is not None else 0
+        if post_weight is not None or add_ids is not None:
+            if pending is not None and (pending.dim() != 2 or pending.dtype != out.dtype
+                                        or not pending.is_contiguous()):
+                raise KernelError("fused_norm: a pending output that is normalised first is dense [rows, H] "
+                                  "of the output's type")
+            if add_table is not None:
+                vocab = add_table.shape[0]
+            if self.timing is not None:
+                e = out.element_size()
+                self._costs(n * H * (2 * e + (4 if resid is not None else 0) + (4 if write_resid else 0)
+                                     + (e if add_ids is not None or table is not None else 0)))
+            self._call("norm", "q3_fused_post_norm", "fused_post_norm", _dtype_code(out.dtype), _ptr(pending),
+                       _ptr(post_weight), float(post_eps), _ptr(resid), _ptr(ids), _ptr(table), _ptr(add_ids),
+                       _ptr(add_table), _ptr(rows), _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)),
+                       vocab)
+            return out
         parts = stride = 0
         if pending is not None and pending.dim() == 3:
             if pending.dtype != torch.float32 or pending.stride(2) != 1 or pending.stride(1) != H:
@@ -289,6 +334,154 @@ class CudaOps:
             self._costs(3 * out.shape[0] * I * out.element_size())
         self._call("norm", "q3_silu_mul", "silu_mul",
                    _dtype_code(out.dtype), _ptr(gate_up), _ptr(out), out.shape[0], I)
+        return out
+
+    def clamped_glu(self, gate_up, out, *, limit, alpha, up_offset):
+        """``out = g * sigmoid(alpha g) * (u + up_offset)`` with ``g = min(gate, limit)`` and
+        ``u = clamp(up, -limit, limit)``; rows of ``gate_up`` are ``[gate | up]`` (csrc/norm.cu)."""
+        F = out.shape[-1]
+        if gate_up.shape[-1] != 2 * F or not gate_up.is_contiguous() or not out.is_contiguous():
+            raise KernelError("clamped_glu: dense [rows, 2F] in, dense [rows, F] out")
+        if self.timing is not None:
+            self._costs(3 * out.shape[0] * F * out.element_size())
+        self._call("norm", "q3_clamped_glu", "clamped_glu", _dtype_code(out.dtype), _ptr(gate_up), _ptr(out),
+                   out.shape[0], F, float(limit), float(alpha), float(up_offset))
+        return out
+
+    # ---- attention through a latent (csrc/latent_attention.cu, csrc/head_gemm.cu) ---------------
+    def latent_norm_rope_store(self, down, *, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, inv_freq, positions,
+                               token_seq, block_table, pages, page_size, write, q_out):
+        """Rows of ``down`` are ``[query latent | key latent | shared key part]``: the query latent is
+        RMS-normalised into ``q_out``; the key latent is RMS-normalised, the key part rotated
+        (interleaved pairs, angle ``position * inv_freq[i]``), and both are written into the token's
+        row of ``pages`` ``[pages, page_size, kv_rank + rot_dim]``."""
+        T = down.shape[0]
+        if down.stride(1) != 1 or down.shape[1] != q_rank + kv_rank + rot_dim or not q_out.is_contiguous():
+            raise KernelError("latent_norm_rope_store: rows of q_rank + kv_rank + rot_dim elements")
+        if pages is not None and (pages.shape[-1] != kv_rank + rot_dim or not pages.is_contiguous()):
+            raise KernelError("latent_norm_rope_store: pages are dense [pages, page_size, kv_rank + rot_dim]")
+        pairs = inv_freq.numel() if inv_freq is not None else 0
+        if self.timing is not None:
+            self._costs(2 * T * (q_rank + kv_rank + rot_dim) * down.element_size())
+        self._call("latent_attention", "q3_latent_norm_rope_store", "latent_norm_rope_store",
+                   _dtype_code(down.dtype), _ptr(down), down.stride(0), q_rank, kv_rank, rot_dim, _ptr(q_weight),
+                   _ptr(kv_weight), float(eps), _ptr(inv_freq), pairs, _ptr(positions), _ptr(token_seq),
+                   _ptr(block_table), block_table.shape[1] if block_table is not None else 0, _ptr(pages),
+                   page_size, T, int(bool(write)), _ptr(q_out))
+
+    @staticmethod
+    def _head_strides(x, what):
+        if x.dim() != 3 or x.stride(2) != 1:
+            raise KernelError(f"{what}: [tokens, heads, n] with unit stride along n")
+        return x.stride(0), x.stride(1)
+
+    def rotate_heads(self, x, out, *, positions, inv_freq):
+        """``out[t, h] = rotate(x[t, h])`` by the token's position (interleaved pairs; elements beyond
+        ``2 * len(inv_freq)`` are copied).  ``x`` and ``out`` may be slices of wider rows."""
+        T, H, n = x.shape
+        xs, os_ = self._head_strides(x, "rotate_heads"), self._head_strides(out, "rotate_heads")
+        pairs = inv_freq.numel() if inv_freq is not None else 0
+        self._call("latent_attention", "q3_rotate_heads", "rotate_heads", _dtype_code(x.dtype), _ptr(x), xs[0], xs[1],
+                   _ptr(out), os_[0], os_[1], _ptr(positions), _ptr(inv_freq), pairs, n, H, T)
+        return out
+
+    def head_linear(self, x, weight, out):
+        """``out[t, h] = weight[h] @ x[t, h]``: ``x`` ``[T, H, K]``, ``weight`` ``[H, N, K]`` dense, ``out``
+        ``[T, H, N]``; ``x`` and ``out`` may be slices of wider rows (csrc/head_gemm.cu)."""
+        T, H, K = x.shape
+        N = weight.shape[1]
+        if weight.shape != (H, N, K) or not weight.is_contiguous() or out.shape != (T, H, N) \
+                or weight.dtype != x.dtype or out.dtype != x.dtype:
+            raise KernelError(f"head_linear: x {list(x.shape)}, weight {list(weight.shape)}, out {list(out.shape)}")
+        xs, os_ = self._head_strides(x, "head_linear"), self._head_strides(out, "head_linear")
+        if self.timing is not None:
+            e = x.element_size()
+            self._costs((H * N * K + T * H * (K + N)) * e, 2.0 * T * H * N * K, f" {T}x{H}x{K}->{N}")
+        self._call("head_gemm", "q3_head_linear", "head_linear", _dtype_code(x.dtype), _ptr(x), xs[0], xs[1],
+                   _ptr(weight), _ptr(out), os_[0], os_[1], T, H, N, K)
+        return out
+
+    def latent_attention(self, q, *, pages, value_dim, block_table, token_seq, positions, sink, out, page_size, scale,
+                         window, step=None):
+        """Causal attention of every token over its sequence's cached rows, all heads sharing them:
+        ``q`` ``[T, H, width]`` already in the rows' space, ``pages`` ``[pages, page_size, width]``, the
+        value of a row its first ``value_dim`` elements, ``out`` ``[T, H, value_dim]``.  ``sink``
+        (float32 ``[H]`` or None) joins the softmax denominator; ``window``: a query sees itself and the
+        ``window - 1`` rows before it."""
+        T, H, width = q.shape
+        if pages.shape[-1] != width or not pages.is_contiguous() or out.shape != (T, H, value_dim):
+            raise KernelError("latent_attention: pages are dense [pages, page_size, width of q]")
+        qs, os_ = self._head_strides(q, "latent_attention"), self._head_strides(out, "latent_attention")
+        if self.timing is not None and step is not None:
+            e = out.element_size()
+            keys = pairs = 0
+            cu = step.host_cu_seqlens
+            for b, kv in enumerate(step.host_kv_lens):
+                n = cu[b + 1] - cu[b] if len(cu) > b + 1 else 1
+                seen = min(kv, (window or kv) + n - 1)
+                keys += seen
+                pairs += sum(min(kv - n + i + 1, window or kv) for i in range(n)) if n < 64 else \
+                    n * min(kv, window or kv)
+            self._costs(keys * width * e + T * H * (width + value_dim) * e, 2.0 * H * (width + value_dim) * pairs)
+        self._call("latent_attention", "q3_latent_attention", "latent_attention", _dtype_code(out.dtype), _ptr(q),
+                   qs[0], qs[1], _ptr(pages), width, value_dim, _ptr(block_table), block_table.shape[1],
+                   _ptr(token_seq), _ptr(positions), _ptr(sink), _ptr(out), os_[0], os_[1], T, H, page_size,
+                   float(scale), int(window or 0))
+        return out
+
+    # ---- routed experts (csrc/experts.cu) --------------------------------------------------------
+    def route_top(self, h, router, top, renormalize=False):
+        """``(chosen int32 [T, top], weights float32 [T, top])``: sigmoid of the float32 router
+        product, the ``top`` largest per token (lowest index on a tie), in descending order."""
+        T, W = h.shape
+        E = router.shape[0]
+        if router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != W or h.stride(1) != 1:
+            raise KernelError("route_top: a dense float32 router [experts, width]")
+        chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+        if self.timing is not None:
+            self._costs(E * W * 4 + T * W * h.element_size(), 2.0 * T * E * W)
+        self._call("experts", "q3_route_top", "route_top", _dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(router),
+                   T, E, W, top, int(bool(renormalize)), _ptr(chosen), _ptr(weights))
+        return chosen, weights
+
+    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit, alpha, up_offset, weight_on="input",
+                       shared=None):
+        """Every token through its chosen experts: ``gate_up`` ``[E, 2F, W]`` (gate rows, then up
+        rows), ``down`` ``[E, W, F]``; the slots are grouped by expert on the device, each expert's two
+        products run over its slots only, and a token's results (and ``shared`` ``[T, W]``) are summed
+        in float32."""
+        T, W = h.shape
+        E, F2, _ = gate_up.shape
+        F, top = F2 // 2, chosen.shape[1]
+        S = T * top
+        dev = h.device
+        if not (gate_up.is_contiguous() and down.is_contiguous() and down.shape == (E, W, F) and h.stride(1) == 1):
+            raise KernelError("routed_experts: dense gate_up [E, 2F, W] and down [E, W, F]")
+        if shared is not None and (shared.shape != (T, W) or not shared.is_contiguous() or shared.dtype != h.dtype):
+            raise KernelError("routed_experts: the shared expert's result is dense [tokens, width]")
+        plan = torch.empty(2 * (E + 1) + S, dtype=torch.int32, device=dev)
+        offsets, tile_offsets, order = plan[: E + 1], plan[E + 1: 2 * (E + 1)], plan[2 * (E + 1):]
+        self._call("experts", "q3_group_slots", "group_slots", _ptr(chosen), S, E, _ptr(offsets), _ptr(tile_offsets),
+                   _ptr(order))
+        mid = torch.empty((S, F), dtype=h.dtype, device=dev)
+        y = torch.empty((S, W), dtype=h.dtype, device=dev)
+        out = torch.empty((T, W), dtype=h.dtype, device=dev)
+        code, e = _dtype_code(h.dtype), h.element_size()
+        on_input = weight_on == "input"
+        if self.timing is not None:  # every chosen expert's weights once, or once per slot when slots are few
+            self._costs(min(S, E) * 2 * F * W * e + T * W * e + S * F * e, 4.0 * S * F * W, f" {S}x{W}->2x{F}")
+        self._call("experts", "q3_expert_gate_up", "expert_gate_up", code, _ptr(h), h.stride(0), _ptr(gate_up),
+                   _ptr(mid), S, E, F, W, top, _ptr(offsets), _ptr(tile_offsets), _ptr(order), _ptr(weights),
+                   int(on_input), float(limit), float(alpha), float(up_offset))
+        if self.timing is not None:
+            self._costs(min(S, E) * F * W * e + S * (F + W) * e, 2.0 * S * F * W, f" {S}x{F}->{W}")
+        self._call("experts", "q3_expert_down", "expert_down", code, _ptr(mid), _ptr(down), _ptr(y), S, E, F, W,
+                   _ptr(offsets), _ptr(tile_offsets), _ptr(order))
+        if self.timing is not None:
+            self._costs((S + T + (T if shared is not None else 0)) * W * e)
+        self._call("experts", "q3_expert_combine", "expert_combine", code, _ptr(y),
+                   None if on_input else _ptr(weights), _ptr(shared), _ptr(out), T, W, top)
         return out
 
     # ---- position encoding + cache write -----------------------------------------------

@@ -33,7 +33,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (must divide 64)")
-    parser.add_argument("--max-live", type=int, default=8, help="state slots: most requests live at a time")
+    parser.add_argument("--max-live", type=int, default=4, help="state slots: most requests live at a time")
     parser.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=None,
                         help="replay captured graphs for decode-only steps (default: as serving does)")
     args = parser.parse_args(argv)
