@@ -39,6 +39,10 @@ kinds and a roofline fraction per kind):
                    [64, 4096] and 256 output tokens, token budgets 2048 and 8192;
 * ``32b``          Qwen3-32B sizes: decode at B = 1 / 8 / 32 behind 1,024-id prompts and one
                    2,048-token prefill (device-timed), and B = 8 end to end;
+* ``logesun``      the Logesun design at two layer sizes (four layers each, random weights) beside a
+                   Qwen3 dense model of equal width, heads and active feed-forward width: one
+                   2,048-token prefill and decode steps at batch 8 behind 1,024-token contexts, both
+                   device-timed through the step function, with the per-kernel table of each;
 * ``decode``, ``latency``, ``batch8``, ``throughput``, ``prefill``, ``longctx``: the six closed
                    batches of the reference's own harness (bench/workloads.py:34-43) at Qwen3-4B
                    sizes, with its token budget rule (bench/workloads.py:52-64).
@@ -89,7 +93,18 @@ BASELINE_TOK_S = 693.26
 # (concurrency = requests, prompt tokens, output tokens) of the reference's closed batches
 CLOSED_CASES = {"decode": (1, 256, 512), "latency": (1, 512, 128), "batch8": (8, 256, 128),
                 "throughput": (16, 256, 128), "prefill": (1, 2048, 16), "longctx": (1, 8192, 64)}
-WORKLOADS = ("default", "decode512", "batch48", "32b", *CLOSED_CASES)
+WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", *CLOSED_CASES)
+
+# Layer sizes for the Logesun design (attention through a latent with a window and a sink, routed
+# clamped experts with a shared one, norms around every sublayer) that resemble real models of that
+# kind, and beside each a Qwen3 dense model of equal width, heads, layers and active feed-forward
+# width.  Four layers each: one with a dense feed-forward, three routed.
+LOGESUN_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, window=1024,
+                  dense_ff=8192, experts=64, top=6, expert_ff=1408, shared_ff=2816, layers=4, vocab=32000),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, window=2048,
+                  dense_ff=12288, experts=32, top=4, expert_ff=2048, shared_ff=2048, layers=4, vocab=32000),
+}
 
 
 def peaks() -> dict:
@@ -556,6 +571,81 @@ def workload_prompts(name: str, np):
     return out
 
 
+def _logesun_config(z: dict):
+    from qwen3_runtime_b200.config import LogesunConfig
+    from qwen3_runtime_b200.config.logesun_config import (ExpertConfig, FeedForwardConfig, LatentAttentionConfig,
+                                                          LogesunLayerConfig)
+
+    mixer = LatentAttentionConfig(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"],
+                                  q_rank=z["q_rank"], kv_rank=z["kv_rank"], scale=(z["dim"] + z["rot_dim"]) ** -0.5,
+                                  rot_dims=z["rot_dim"], rot_base=10000.0, window=z["window"])
+    dense = FeedForwardConfig(kind="dense", ff=z["dense_ff"])
+    moe = FeedForwardConfig(kind="moe", experts=z["experts"], top=z["top"], expert=ExpertConfig(z["expert_ff"], 7.0),
+                            shared=ExpertConfig(z["shared_ff"], 7.0))
+    layers = tuple(LogesunLayerConfig("latent_attention", mixer, dense if i == 0 else moe) for i in range(z["layers"]))
+    return LogesunConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, layers=layers)
+
+
+def _dense_twin_config(z: dict):
+    from qwen3_runtime_b200.config import Qwen3Config
+
+    active = z["top"] * z["expert_ff"] + z["shared_ff"]
+    return Qwen3Config(vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
+                       num_attention_heads=z["heads"], num_key_value_heads=max(1, z["heads"] // 4), head_dim=128,
+                       intermediate_size=-(-active // 128) * 128, rms_norm_eps=1e-6, rope_theta=1e6,
+                       max_position_embeddings=8192, tie_word_embeddings=False)
+
+
+def run_logesun(args, pk) -> dict:
+    """Prefill and decode of the Logesun design beside a Qwen3 dense model of equal size."""
+    import torch
+
+    from qwen3_runtime_b200.engine.factory import build_model, build_runtime
+    from qwen3_runtime_b200.ops.cuda import CudaOps
+    from qwen3_runtime_b200.weights.random_init import RandomDeviceSource, expected_tensors_for
+
+    torch.cuda.set_device(0)
+    K, W = max(8, args.steps // 2), args.warmup
+    batch, context = BATCH, 1024
+    rand_ids = make_rand_ids(torch)
+    clocks = ClockSampler().start()
+    results = {}
+    for size, z in LOGESUN_SIZES.items():
+        for arm, cfg in (("logesun", _logesun_config(z)), ("qwen3_dense", _dense_twin_config(z))):
+            ops = CudaOps()
+            model = build_model(cfg, RandomDeviceSource(expected_tensors_for(cfg), SEED, "cuda"), dtype="bfloat16",
+                                ops=ops)
+            tokens = batch * (context + K + W + 64) + PREFILL_TOKENS + 64
+            rt = build_runtime(model, block_size=PAGE, num_kv_blocks=-(-tokens // PAGE) + 64, max_num_seqs=batch + 2,
+                               cuda_graph=True)
+            for t in rt.storage.tensors:
+                t.normal_(0.0, 0.5)
+            ms_steps, launches = decode_point(rt, ops, torch, rand_ids, batch, context, K, W, sampler=clocks)
+            prefill_ms = prefill_point(rt, torch, rand_ids, PREFILL_TOKENS)
+            rt.runner.graphs = None
+            kernels = kernel_table(rt, ops, torch, rand_ids, batch, context, pk)
+            ops.raise_if_kernel_error()
+            results[f"{size}/{arm}"] = dict(
+                decode_tok_s=round(batch * 1000.0 / ms_steps[0], 1), decode_ms_per_step=round(ms_steps[0], 4),
+                prefill_tok_s=round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), prefill_ms=round(prefill_ms, 3),
+                launches_per_decode_step=launches, kernels=kernels)
+            del rt, model, ops
+            torch.cuda.empty_cache()
+    first = results["w2048/logesun"]
+    return {
+        "metric": "decode tok/s @ batch 8, ctx 1024 (Logesun w2048 sizes, 4 layers, bf16); beside it a Qwen3 dense "
+                  "model of equal size, and one 2048-token prefill of each",
+        "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "impl": "ours", "workload": "logesun",
+        "data": "synthetic: seeded random weights N(0,0.02), random token ids; cache pages hold random rows",
+        "config": dict(model="Logesun sizes " + ", ".join(LOGESUN_SIZES), global_batch=batch, seq_len=context,
+                       parallelism="single GPU", sizes=LOGESUN_SIZES,
+                       l2="weights and cache rows of a step exceed L2; no flush"),
+        "results": results, "peaks": pk, "clocks": clocks.summary(),
+    }
+
+
 def run_workload_ours(args) -> dict:
     import numpy as np
     import torch
@@ -563,6 +653,8 @@ def run_workload_ours(args) -> dict:
     pk = peaks()
     if args.workload == "32b":
         return run_32b_ours(args, pk)
+    if args.workload == "logesun":
+        return run_logesun(args, pk)
     cases = workload_prompts(args.workload, np)
     results, cfg, build_s, engine = {}, None, 0.0, None
     clocks = ClockSampler()
@@ -820,6 +912,9 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.workload == "default":
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    elif args.workload == "logesun" and args.impl == "reference":
+        result = {"impl": "reference", "workload": "logesun",
+                  "unavailable": "the reference has no model of this design (it serves Qwen3 dense only)"}
     else:
         result = run_workload_reference(args) if args.impl == "reference" else run_workload_ours(args)
     print(json.dumps(result))

@@ -1,10 +1,10 @@
 // Routed experts: router scores and choice, grouping of (token, choice) slots by expert on the
 // device, the experts' two products over their own slots, and the per-token sum.
 //
-//   route_top      z = W_router h in fp32, s = sigmoid(z), the `top` largest s (lowest index on a
-//                  tie) with their scores as weights (optionally divided by their sum)
+//   route_top      z = W_router h in fp32, the `top` largest z (the order of their sigmoids; lowest
+//                  index on a tie) with sigmoid(z) as weights (optionally divided by their sum)
 //   group_slots    slots sorted by expert: offsets[E + 1], order[S], and for the products the
-//                  first row tile of each expert, tile_offsets[E + 1] (tiles of EXPERT_BM slots)
+//                  first row tile of each expert, tile_offsets[E + 1] (tiles of `bm` slots)
 //   expert_gate_up mid[slot] = glu(W_gate_e x, W_up_e x), x = h[token] * weight (rounded to the
 //                  operand type) when the weight multiplies the expert's input
 //                  glu: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + off)
@@ -15,38 +15,84 @@
 // Products accumulate in fp32 on the FMA pipes, each output one accumulator over ascending k, so a
 // token's result does not depend on which other tokens chose the same expert.  Nothing here reads
 // a count back on the host: grids are sized for the worst case and surplus blocks leave at once.
-#include "common.cuh"
+#include "mma_tiles.cuh"
 
-constexpr int EXPERT_BM = 32;
+constexpr int EXPERT_BM = 32;  // slots per row tile of the FMA products
 
 // ---- router ------------------------------------------------------------------------------------
+// Two kernels.  route_logits: a block stages ROUTE_TT tokens' rows in shared memory as fp32 and each
+// of its eight warps streams one expert's router row once for all of them (a step of a few tokens
+// still spreads the router over E / 8 blocks).  route_pick: one warp per token takes the `top`
+// largest logits -- the choice is made on the logits, which order the experts as their sigmoids do
+// but do not collapse into ties where the sigmoid saturates; lowest index on an exact tie -- and
+// writes sigmoid(logit) as the weight.
+constexpr int ROUTE_TT = 8;
+
 template <typename T>
-__global__ void route_top_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ router, int E,
-                                 int W, int top, int renormalize, int* __restrict__ chosen,
-                                 float* __restrict__ weights) {
-  extern __shared__ float scores[];  // E
+__global__ void __launch_bounds__(256)
+route_logits_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ router, int num_tokens, int E,
+                    int W, float* __restrict__ logits) {
+  extern __shared__ float route_rows[];  // [ROUTE_TT][W]
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  const T* row = h + (long)t * h_stride;
-  for (int e = warp; e < E; e += nwarp) {
-    const float* wr = router + (long)e * W;
-    float dot = 0.f;
-    for (int i = lane; i < W; i += 32) dot = fmaf(to_f32(row[i]), wr[i], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) scores[e] = 1.f / (1.f + expf(-dot));
+  const int t0 = blockIdx.x * ROUTE_TT;
+  const int nt = min(ROUTE_TT, num_tokens - t0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < nt * W; i += 256) {
+    const int t = i / W, k = i - t * W;
+    route_rows[i] = to_f32(h[(long)(t0 + t) * h_stride + k]);
   }
   __syncthreads();
-  if (warp != 0) return;
+  const int e = blockIdx.y * 8 + warp;
+  if (e >= E) return;
+  const float* wr = router + (long)e * W;
+  float acc[ROUTE_TT];
+#pragma unroll
+  for (int t = 0; t < ROUTE_TT; ++t) acc[t] = 0.f;
+  if ((W & 3) == 0) {
+#pragma unroll 2
+    for (int i = lane * 4; i < W; i += 128) {
+      const float4 w4 = *reinterpret_cast<const float4*>(wr + i);
+#pragma unroll
+      for (int t = 0; t < ROUTE_TT; ++t) {
+        if (t < nt) {
+          const float4 x4 = *reinterpret_cast<const float4*>(route_rows + t * W + i);
+          acc[t] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[t]))));
+        }
+      }
+    }
+  } else {
+    for (int i = lane; i < W; i += 32) {
+      const float w1 = wr[i];
+#pragma unroll
+      for (int t = 0; t < ROUTE_TT; ++t)
+        if (t < nt) acc[t] = fmaf(route_rows[t * W + i], w1, acc[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < ROUTE_TT; ++t) {
+    if (t < nt) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) logits[(long)(t0 + t) * E + e] = v;
+    }
+  }
+}
+
+__global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, int E, int top, int renormalize,
+                                  int* __restrict__ chosen, float* __restrict__ weights) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= num_tokens) return;
+  float* z = logits + (long)t * E;
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
+    float best = -INFINITY;
     int at = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float s = scores[e];
-      if (s > best) {
-        best = s;
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) {
+        best = v;
         at = e;
       }
     }
@@ -59,40 +105,52 @@ __global__ void route_top_kernel(const T* __restrict__ h, long h_stride, const f
         at = oa;
       }
     }
+    const float score = 1.f / (1.f + expf(-best));
     if (lane == 0) {
       chosen[(long)t * top + k] = at;
-      weights[(long)t * top + k] = best;
-      scores[at] = -2.f;  // below every sigmoid
+      weights[(long)t * top + k] = score;
+      z[at] = -INFINITY;  // taken
     }
-    total += best;
+    total += score;
     __syncwarp();
   }
   if (renormalize)
     for (int k = lane; k < top; k += 32) weights[(long)t * top + k] /= total;
 }
 
+// logits: fp32 scratch [num_tokens, E] (left with the chosen entries at -inf).
 Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float* router, int num_tokens, int E, int W,
-                           int top, int renormalize, int* chosen, float* weights, cudaStream_t stream) {
-  if (!h || !router || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
-  if (E > 8192) return Q3_ERR_UNSUPPORTED;
+                           int top, int renormalize, float* logits, int* chosen, float* weights,
+                           cudaStream_t stream) {
+  if (!h || !router || !logits || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
-  const size_t smem = (size_t)E * sizeof(float);
+  const size_t smem = (size_t)ROUTE_TT * W * sizeof(float);
+  if (smem > 200 * 1024 || (reinterpret_cast<uintptr_t>(router) & 15) || (E + 7) / 8 > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((num_tokens + ROUTE_TT - 1) / ROUTE_TT, (E + 7) / 8);
   cudaError_t e;
-  if (dtype == Q3_DTYPE_F32)
-    e = launch_pdl(route_top_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (const float*)h, h_stride,
-                   router, E, W, top, renormalize, chosen, weights);
-  else if (dtype == Q3_DTYPE_BF16)
-    e = launch_pdl(route_top_kernel<bf16>, dim3(num_tokens), dim3(128), smem, stream, (const bf16*)h, h_stride, router,
-                   E, W, top, renormalize, chosen, weights);
-  else
+  if (dtype == Q3_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(route_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(route_logits_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, h_stride, router,
+                   num_tokens, E, W, logits);
+  } else if (dtype == Q3_DTYPE_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(route_logits_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(route_logits_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)h, h_stride, router,
+                   num_tokens, E, W, logits);
+  } else {
     return Q3_ERR_ARGUMENT;
+  }
+  if (e != cudaSuccess) return Q3_ERR_LAUNCH;
+  e = launch_pdl(route_pick_kernel, dim3((num_tokens + 3) / 4), dim3(128), 0, stream, logits, num_tokens, E, top,
+                 renormalize, chosen, weights);
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
 // ---- slots grouped by expert ----------------------------------------------------------------------
 // One block, for a few hundred slots.  Slots of one expert keep their order (slot s before slot
 // s' > s), so the grouping is the same on every run.
-__global__ void group_slots_kernel(const int* __restrict__ chosen, int S, int E, int* __restrict__ offsets,
+__global__ void group_slots_kernel(const int* __restrict__ chosen, int S, int E, int bm, int* __restrict__ offsets,
                                    int* __restrict__ tile_offsets, int* __restrict__ order) {
   extern __shared__ int sm[];  // counts[E], cursor[E]
   int* counts = sm;
@@ -110,7 +168,7 @@ __global__ void group_slots_kernel(const int* __restrict__ chosen, int S, int E,
       tile_offsets[e] = tiles;
       cursor[e] = at;
       at += counts[e];
-      tiles += (counts[e] + EXPERT_BM - 1) / EXPERT_BM;
+      tiles += (counts[e] + bm - 1) / bm;
     }
     offsets[E] = at;
     tile_offsets[E] = tiles;
@@ -127,8 +185,9 @@ __global__ void group_slots_kernel(const int* __restrict__ chosen, int S, int E,
 
 // The same for many slots: placement by atomic cursor (the order inside an expert's group may then
 // differ from run to run; every slot's result is computed on its own, so the outputs do not).
-__global__ void group_slots_atomic_kernel(const int* __restrict__ chosen, int S, int E, int* __restrict__ offsets,
-                                          int* __restrict__ tile_offsets, int* __restrict__ order) {
+__global__ void group_slots_atomic_kernel(const int* __restrict__ chosen, int S, int E, int bm,
+                                          int* __restrict__ offsets, int* __restrict__ tile_offsets,
+                                          int* __restrict__ order) {
   extern __shared__ int sm[];
   int* counts = sm;
   int* cursor = sm + E;
@@ -145,7 +204,7 @@ __global__ void group_slots_atomic_kernel(const int* __restrict__ chosen, int S,
       tile_offsets[e] = tiles;
       cursor[e] = at;
       at += counts[e];
-      tiles += (counts[e] + EXPERT_BM - 1) / EXPERT_BM;
+      tiles += (counts[e] + bm - 1) / bm;
     }
     offsets[E] = at;
     tile_offsets[E] = tiles;
@@ -154,17 +213,19 @@ __global__ void group_slots_atomic_kernel(const int* __restrict__ chosen, int S,
   for (int s = threadIdx.x; s < S; s += blockDim.x) order[atomicAdd(&cursor[chosen[s]], 1)] = s;
 }
 
-Q3_EXPORT int q3_group_slots(const int* chosen, int S, int E, int* offsets, int* tile_offsets, int* order,
+// bm: slots per row tile of the products that will use tile_offsets (EXPERT_BM for the FMA kernels).
+Q3_EXPORT int q3_group_slots(const int* chosen, int S, int E, int bm, int* offsets, int* tile_offsets, int* order,
                              cudaStream_t stream) {
-  if (!chosen || !offsets || !tile_offsets || !order || E < 1 || S < 0) return Q3_ERR_ARGUMENT;
+  if (!chosen || !offsets || !tile_offsets || !order || E < 1 || S < 0 || bm < 1) return Q3_ERR_ARGUMENT;
   if (E > 8192) return Q3_ERR_UNSUPPORTED;
   const size_t smem = 2 * (size_t)E * sizeof(int);
   cudaError_t e;
   if (S <= 512)
-    e = launch_pdl(group_slots_kernel, dim3(1), dim3(512), smem, stream, chosen, S, E, offsets, tile_offsets, order);
-  else
-    e = launch_pdl(group_slots_atomic_kernel, dim3(1), dim3(1024), smem, stream, chosen, S, E, offsets, tile_offsets,
+    e = launch_pdl(group_slots_kernel, dim3(1), dim3(512), smem, stream, chosen, S, E, bm, offsets, tile_offsets,
                    order);
+  else
+    e = launch_pdl(group_slots_atomic_kernel, dim3(1), dim3(1024), smem, stream, chosen, S, E, bm, offsets,
+                   tile_offsets, order);
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
@@ -320,6 +381,162 @@ Q3_EXPORT int q3_expert_down(int dtype, const void* mid, const void* down, void*
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- the same products on the tensor cores (bfloat16, mma.sync m16n8k16) ---------------------------
+// A block owns BM slots of one expert and 64 output columns (of gate and of up for GATE_UP); four
+// warps, WM = BM / 32 of them along the slots.  The slots' rows are gathered (and, for GATE_UP with
+// the weight on the input, multiplied by it and rounded to bfloat16) into shared memory, the
+// expert's rows come by cp.async, 32 of the inner dimension at a time.  K is a multiple of 8 and
+// all rows are 16-byte aligned.
+template <bool GATE_UP, int BM>
+__global__ void __launch_bounds__(128)
+expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __restrict__ B, bf16* __restrict__ C,
+                      int N, int K, const int* __restrict__ offsets, const int* __restrict__ tile_offsets,
+                      const int* __restrict__ order, const float* __restrict__ weights, int E, int top,
+                      int scale_input, float limit, float alpha, float up_offset) {
+  constexpr int BN = 64, BK = 32, KS = BK + 8, NB = GATE_UP ? 2 : 1;
+  constexpr int WM = BM / 32, WN = 4 / WM, COLS = BN / WN, NTW = COLS / 8;
+  __shared__ __align__(16) bf16 As[BM][KS];
+  __shared__ __align__(16) bf16 Ws[NB][BN][KS];
+  __shared__ int slot_of[BM];
+  __shared__ float scale_of[BM];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tile = blockIdx.y;
+  if (tile >= tile_offsets[E]) return;
+  const int e = expert_of_tile(tile_offsets, E, tile);
+  const int row0 = offsets[e] + (tile - tile_offsets[e]) * BM;
+  const int rows = min(BM, offsets[e + 1] - row0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int r = tid; r < BM; r += 128) {
+    const int slot = r < rows ? order[row0 + r] : -1;
+    slot_of[r] = slot;
+    scale_of[r] = (slot >= 0 && GATE_UP && scale_input) ? weights[slot] : 1.f;
+  }
+  __syncthreads();
+  const int wm = warp / WN, wn = warp % WN;
+  const int n0 = blockIdx.x * BN;
+  const bf16* Be = B + (long)e * NB * N * K;
+  float acc[NB][2][NTW][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[b][mt][nt][x] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int c = tid; c < NB * BN * (BK / 8); c += 128) {
+      const int b = c / (BN * (BK / 8)), y = c % (BN * (BK / 8));
+      const int r = y / (BK / 8), ch = y % (BK / 8);
+      const int gn = n0 + r, gk = k0 + ch * 8;
+      const bool in = gn < N && gk < K;
+      cp_async16(smem_u32(&Ws[b][r][ch * 8]), in ? Be + ((long)b * N + gn) * K + gk : Be, in ? 16 : 0);
+    }
+    cp_async_commit();
+    for (int c = tid; c < BM * (BK / 8); c += 128) {
+      const int r = c / (BK / 8), ch = c % (BK / 8);
+      const int slot = slot_of[r], gk = k0 + ch * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (slot >= 0 && gk < K) {
+        const long arow = GATE_UP ? slot / top : slot;
+        v = *reinterpret_cast<const uint4*>(A + arow * a_stride + gk);
+        if (GATE_UP && scale_input) {
+          __nv_bfloat162* hv = reinterpret_cast<__nv_bfloat162*>(&v);
+          const float w = scale_of[r];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float2 f = __bfloat1622float2(hv[x]);
+            hv[x] = __floats2bfloat162_rn(f.x * w, f.y * w);
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(&As[r][ch * 8]) = v;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        ldmatrix_x4(a[mt], smem_u32(&As[wm * 32 + mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int np = 0; np < NTW / 2; ++np) {
+          uint32_t bb[4];
+          ldmatrix_x4(bb, smem_u32(&Ws[b][wn * COLS + np * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16(acc[b][mt][2 * np], a[mt], bb[0], bb[1]);
+            mma_bf16(acc[b][mt][2 * np + 1], a[mt], bb[2], bb[3]);
+          }
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int slot = slot_of[wm * 32 + mt * 16 + half * 8 + (lane >> 2)];
+      if (slot < 0) continue;
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int gn = n0 + wn * COLS + nt * 8 + 2 * (lane & 3) + x;
+          if (gn >= N) continue;
+          if (GATE_UP) {
+            const float g = fminf(to_f32(from_f32<bf16>(acc[0][mt][nt][2 * half + x])), limit);
+            const float u = fminf(fmaxf(to_f32(from_f32<bf16>(acc[NB - 1][mt][nt][2 * half + x])), -limit), limit);
+            C[(long)slot * N + gn] = from_f32<bf16>((g / (1.f + expf(-alpha * g))) * (u + up_offset));
+          } else {
+            C[(long)slot * N + gn] = from_f32<bf16>(acc[0][mt][nt][2 * half + x]);
+          }
+        }
+    }
+}
+
+// The two products as above for bfloat16 with rows of 16-byte multiples; bm (32 or 64) is the row
+// tile that group_slots was given.
+Q3_EXPORT int q3_expert_gate_up_tc(const void* h, long h_stride, const void* gate_up, void* mid, int S, int E, int F,
+                                   int W, int top, int bm, const int* offsets, const int* tile_offsets,
+                                   const int* order, const float* weights, int scale_input, float limit, float alpha,
+                                   float up_offset, cudaStream_t stream) {
+  if (!h || !gate_up || !mid || !offsets || !tile_offsets || !order || !weights) return Q3_ERR_ARGUMENT;
+  if (E < 1 || F < 1 || W < 1 || top < 1 || (bm != 32 && bm != 64)) return Q3_ERR_ARGUMENT;
+  if (W % 8 || h_stride % 8 || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(gate_up) & 15))
+    return Q3_ERR_UNSUPPORTED;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / bm + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((F + 63) / 64, tiles);
+  auto kernel = bm == 64 ? expert_gemm_tc_kernel<true, 64> : expert_gemm_tc_kernel<true, 32>;
+  return launch_pdl(kernel, grid, dim3(128), 0, stream, (const bf16*)h, h_stride, (const bf16*)gate_up, (bf16*)mid, F,
+                    W, offsets, tile_offsets, order, weights, E, top, scale_input, limit, alpha, up_offset) == cudaSuccess
+             ? Q3_OK
+             : Q3_ERR_LAUNCH;
+}
+
+Q3_EXPORT int q3_expert_down_tc(const void* mid, const void* down, void* y, int S, int E, int F, int W, int bm,
+                                const int* offsets, const int* tile_offsets, const int* order, cudaStream_t stream) {
+  if (!mid || !down || !y || !offsets || !tile_offsets || !order || E < 1 || F < 1 || W < 1) return Q3_ERR_ARGUMENT;
+  if (bm != 32 && bm != 64) return Q3_ERR_ARGUMENT;
+  if (F % 8 || (reinterpret_cast<uintptr_t>(mid) & 15) || (reinterpret_cast<uintptr_t>(down) & 15))
+    return Q3_ERR_UNSUPPORTED;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / bm + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((W + 63) / 64, tiles);
+  auto kernel = bm == 64 ? expert_gemm_tc_kernel<false, 64> : expert_gemm_tc_kernel<false, 32>;
+  return launch_pdl(kernel, grid, dim3(128), 0, stream, (const bf16*)mid, (long)F, (const bf16*)down, (bf16*)y, W, F,
+                    offsets, tile_offsets, order, (const float*)nullptr, E, 1, 0, 0.f, 0.f, 0.f) == cudaSuccess
+             ? Q3_OK
+             : Q3_ERR_LAUNCH;
 }
 
 // ---- per-token sum ----------------------------------------------------------------------------------

@@ -359,7 +359,8 @@ static int launch_fused_post_norm(const void* pending, const float* post_w, floa
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(fused_post_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+  int threads = ((H / 4 + 31) / 32) * 32;  // about four elements a thread: the row's loads are all in flight at once
+  threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
   return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending, post_w,
                     post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, rows, w, (T*)out, H, eps,
                     write_resid, vocab) == cudaSuccess

@@ -69,14 +69,23 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_float, c_int,
                                 c_void_p],
     },
+    "latent_attention_tc": {
+        "q3_latent_attention_tc": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_float,
+                                   c_int, c_int, c_void_p, c_void_p],
+    },
     "head_gemm": {
         "q3_head_linear": [c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int,
                            c_int, c_void_p],
     },
     "experts": {
         "q3_route_top": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                         c_void_p],
-        "q3_group_slots": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                         c_void_p, c_void_p],
+        "q3_group_slots": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "q3_expert_gate_up_tc": [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p],
+        "q3_expert_down_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                              c_void_p, c_void_p],
         "q3_expert_gate_up": [c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p],
         "q3_expert_down": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
@@ -181,6 +190,8 @@ class CudaOps:
         self.prefill_attention = "tcgen05"  # "mma" keeps every prompt portion on the mma.sync kernel
         self.tcgen05_pairs = True           # False: the tcgen05 product never pairs SMs (cta_group::1 only)
         self.fuse_decode_new_token = True   # False: always the separate q/k norm + rotation + store kernel
+        self.latent_attention_tc = True     # False: attention over latent rows always on the general kernel
+        self.experts_tc = True              # False: the experts' products always on the FMA kernels
         self._tickets: torch.Tensor | None = None
         self._argmax_tickets: torch.Tensor | None = None
         # products of at most 16 tokens: "auto" -- the shared-memory stream (csrc/gemm_stream.cu) for the
@@ -397,6 +408,14 @@ class CudaOps:
         if self.timing is not None:
             e = x.element_size()
             self._costs((H * N * K + T * H * (K + N)) * e, 2.0 * T * H * N * K, f" {T}x{H}x{K}->{N}")
+        if x.dtype == torch.bfloat16 and T > self.SMALL_M:
+            # more than 16 tokens in bfloat16: the library's batched product, as for plain products
+            if self.timing is not None:
+                with self._timed("library_bmm"):
+                    torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+            else:
+                torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+            return out
         self._call("head_gemm", "q3_head_linear", "head_linear", _dtype_code(x.dtype), _ptr(x), xs[0], xs[1],
                    _ptr(weight), _ptr(out), os_[0], os_[1], T, H, N, K)
         return out
@@ -423,6 +442,30 @@ class CudaOps:
                 pairs += sum(min(kv - n + i + 1, window or kv) for i in range(n)) if n < 64 else \
                     n * min(kv, window or kv)
             self._costs(keys * width * e + T * H * (width + value_dim) * e, 2.0 * H * (width + value_dim) * pairs)
+        if (self.latent_attention_tc and step is not None and out.dtype == torch.bfloat16 and width % 16 == 0
+                and value_dim % 16 == 0 and value_dim <= 512 and qs[0] % 8 == 0 and qs[1] % 8 == 0
+                and os_[0] % 2 == 0 and os_[1] % 2 == 0 and q.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0
+                and out.data_ptr() % 4 == 0 and (32 + 64) * (width + 8) * 2 + 14000 <= 220 * 1024):
+            # bfloat16 on the tensor cores: 32 (token, head) rows per block, keys in tiles of 64
+            splits, part = 1, None
+            if step.max_query_len == 1:
+                # few rows, many keys: cut every sequence's keys into slices so that about two blocks
+                # per SM work.  The count comes from an upper bound of the lengths (in a captured step:
+                # the block-table width it was captured for), never from the lengths of the moment.
+                bound = step.captured_width * page_size or step.max_kv_len
+                if window:
+                    bound = min(bound, int(window) + 63)
+                groups = -(-H // min(32, 1 << max(0, (H - 1).bit_length())))
+                splits = max(1, min(-(-bound // 64), 2 * self.SM_COUNT // max(1, step.num_seqs * groups), 64))
+                if splits > 1:
+                    part = torch.empty(step.num_seqs * H * splits * (value_dim + 2), dtype=torch.float32,
+                                       device=out.device)
+                    self.launches += 1  # the merge of the slices
+            self._call("latent_attention_tc", "q3_latent_attention_tc", "latent_attention_tc", _ptr(q), qs[0], qs[1],
+                       _ptr(pages), width, value_dim, _ptr(block_table), block_table.shape[1], _ptr(step.cu_seqlens),
+                       _ptr(step.kv_lens), _ptr(sink), _ptr(out), os_[0], os_[1], step.num_seqs,
+                       step.max_query_len, H, page_size, float(scale), int(window or 0), splits, _ptr(part))
+            return out
         self._call("latent_attention", "q3_latent_attention", "latent_attention", _dtype_code(out.dtype), _ptr(q),
                    qs[0], qs[1], _ptr(pages), width, value_dim, _ptr(block_table), block_table.shape[1],
                    _ptr(token_seq), _ptr(positions), _ptr(sink), _ptr(out), os_[0], os_[1], T, H, page_size,
@@ -431,18 +474,22 @@ class CudaOps:
 
     # ---- routed experts (csrc/experts.cu) --------------------------------------------------------
     def route_top(self, h, router, top, renormalize=False):
-        """``(chosen int32 [T, top], weights float32 [T, top])``: sigmoid of the float32 router
-        product, the ``top`` largest per token (lowest index on a tie), in descending order."""
+        """``(chosen int32 [T, top], weights float32 [T, top])``: the float32 router product, the
+        ``top`` largest per token in descending order (chosen on the logits, which order the experts as
+        their sigmoids do without the ties of a saturated sigmoid; lowest index on an exact tie), with
+        the sigmoids as weights."""
         T, W = h.shape
         E = router.shape[0]
         if router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != W or h.stride(1) != 1:
             raise KernelError("route_top: a dense float32 router [experts, width]")
         chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+        logits = torch.empty((T, E), dtype=torch.float32, device=h.device)
         if self.timing is not None:
             self._costs(E * W * 4 + T * W * h.element_size(), 2.0 * T * E * W)
+        self.launches += 1  # two kernels: the logits, then the choice
         self._call("experts", "q3_route_top", "route_top", _dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(router),
-                   T, E, W, top, int(bool(renormalize)), _ptr(chosen), _ptr(weights))
+                   T, E, W, top, int(bool(renormalize)), _ptr(logits), _ptr(chosen), _ptr(weights))
         return chosen, weights
 
     def routed_experts(self, h, chosen, weights, gate_up, down, *, limit, alpha, up_offset, weight_on="input",
@@ -462,8 +509,13 @@ class CudaOps:
             raise KernelError("routed_experts: the shared expert's result is dense [tokens, width]")
         plan = torch.empty(2 * (E + 1) + S, dtype=torch.int32, device=dev)
         offsets, tile_offsets, order = plan[: E + 1], plan[E + 1: 2 * (E + 1)], plan[2 * (E + 1):]
-        self._call("experts", "q3_group_slots", "group_slots", _ptr(chosen), S, E, _ptr(offsets), _ptr(tile_offsets),
-                   _ptr(order))
+        # bfloat16 with 16-byte rows: the products run on the tensor cores, in row tiles of 64 slots when
+        # an expert gets about that many, else of 32
+        tensor_cores = (self.experts_tc and h.dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0
+                        and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
+        bm = 64 if tensor_cores and S >= 48 * E else 32
+        self._call("experts", "q3_group_slots", "group_slots", _ptr(chosen), S, E, bm, _ptr(offsets),
+                   _ptr(tile_offsets), _ptr(order))
         mid = torch.empty((S, F), dtype=h.dtype, device=dev)
         y = torch.empty((S, W), dtype=h.dtype, device=dev)
         out = torch.empty((T, W), dtype=h.dtype, device=dev)
@@ -471,13 +523,22 @@ class CudaOps:
         on_input = weight_on == "input"
         if self.timing is not None:  # every chosen expert's weights once, or once per slot when slots are few
             self._costs(min(S, E) * 2 * F * W * e + T * W * e + S * F * e, 4.0 * S * F * W, f" {S}x{W}->2x{F}")
-        self._call("experts", "q3_expert_gate_up", "expert_gate_up", code, _ptr(h), h.stride(0), _ptr(gate_up),
-                   _ptr(mid), S, E, F, W, top, _ptr(offsets), _ptr(tile_offsets), _ptr(order), _ptr(weights),
-                   int(on_input), float(limit), float(alpha), float(up_offset))
+        if tensor_cores:
+            self._call("experts", "q3_expert_gate_up_tc", "expert_gate_up_tc", _ptr(h), h.stride(0), _ptr(gate_up),
+                       _ptr(mid), S, E, F, W, top, bm, _ptr(offsets), _ptr(tile_offsets), _ptr(order), _ptr(weights),
+                       int(on_input), float(limit), float(alpha), float(up_offset))
+        else:
+            self._call("experts", "q3_expert_gate_up", "expert_gate_up", code, _ptr(h), h.stride(0), _ptr(gate_up),
+                       _ptr(mid), S, E, F, W, top, _ptr(offsets), _ptr(tile_offsets), _ptr(order), _ptr(weights),
+                       int(on_input), float(limit), float(alpha), float(up_offset))
         if self.timing is not None:
             self._costs(min(S, E) * F * W * e + S * (F + W) * e, 2.0 * S * F * W, f" {S}x{F}->{W}")
-        self._call("experts", "q3_expert_down", "expert_down", code, _ptr(mid), _ptr(down), _ptr(y), S, E, F, W,
-                   _ptr(offsets), _ptr(tile_offsets), _ptr(order))
+        if tensor_cores:
+            self._call("experts", "q3_expert_down_tc", "expert_down_tc", _ptr(mid), _ptr(down), _ptr(y), S, E, F, W,
+                       bm, _ptr(offsets), _ptr(tile_offsets), _ptr(order))
+        else:
+            self._call("experts", "q3_expert_down", "expert_down", code, _ptr(mid), _ptr(down), _ptr(y), S, E, F, W,
+                       _ptr(offsets), _ptr(tile_offsets), _ptr(order))
         if self.timing is not None:
             self._costs((S + T + (T if shared is not None else 0)) * W * e)
         self._call("experts", "q3_expert_combine", "expert_combine", code, _ptr(y),

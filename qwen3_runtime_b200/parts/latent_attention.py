@@ -88,6 +88,8 @@ class LatentAttention(Part):
             groups.append("gemm_f32")
         else:
             groups += ["gemm_small_m", "gemm_stream"]
+            if self.row_width % 16 == 0 and self.kv_rank % 16 == 0 and self.kv_rank <= 512:
+                groups.append("latent_attention_tc")
         return groups
 
     def cache_spec(self):

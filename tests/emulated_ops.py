@@ -174,9 +174,8 @@ class TorchOps:
 
     # ---- routed experts ----------------------------------------------------------------
     def route_top(self, h, router, top, renormalize=False):
-        scores = torch.sigmoid(h.float() @ router.float().t())
-        best = torch.topk(scores, top, dim=-1)
-        w = best.values
+        best = torch.topk(h.float() @ router.float().t(), top, dim=-1)  # on the logits: no saturated ties
+        w = torch.sigmoid(best.values)
         if renormalize:
             w = w / w.sum(-1, keepdim=True)
         return best.indices.to(torch.int32), w.float()

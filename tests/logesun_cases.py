@@ -70,7 +70,7 @@ CONFIGS = {
 STD = 0.15  # spread of the random matrices: attention and the experts' clamps have to matter
 
 
-ROUTER_GAIN = 8.0  # routers are made decisive, so that a choice does not hang on the last bit of a score
+ROUTER_GAIN = 3.0  # routers are made decisive (a choice should not hang on a score's last bit) but do not saturate
 
 
 def make_dir(tmp_path, name, sink_scale=1.0):
@@ -182,7 +182,8 @@ def case_sink_matters(tmp_path, name, dtype, ops, device):
     base, _ = expected(make_dir(tmp_path, name), requests, "float32")
     folder = make_dir(tmp_path, name, sink_scale=10.0)
     want, tol = expected(folder, requests, dtype)
-    assert float((want["r0"] - base["r0"]).abs().max()) > 50 * tol, "the sinks hardly change this model"
+    exact, tol32 = expected(folder, requests, "float32")
+    assert float((exact["r0"] - base["r0"]).abs().max()) > 1000 * tol32, "the sinks hardly change this model"
     rt = runtime(folder, name, dtype, ops, device, pages=32)
     check(run_trace(rt, trace_portions(requests, seed=2)), want, tol, f"{name} {dtype} large sinks")
 
@@ -295,7 +296,8 @@ def case_attention_edges(dtype, ops, device, *, window=12, page_size=8, heads=3,
     pages_needed = -(-T // page_size)
     table = list(reversed(range(1, pages_needed + 1)))
     sink = torch.tensor([0.5, -1.0, 2.0][:heads])
-    cases = [(win, qi, qi - dist) for win in (window,) for qi in (31, 32, 36, T - 1) for dist in (win - 1, win)]
+    cases = [(win, qi, qi - dist) for win in (window,) for qi in (win + 19, win + 20, win + 24, T - 1)
+             for dist in (win - 1, win)]
     cases += [(None, T - 1, 1), (None, 20, 0)]
     for win, qi, kj in cases:
         rows = (0.3 * torch.randn((T, width), generator=gen))
