@@ -148,7 +148,7 @@ class LogesunConfig:
             raise ConfigError(f"norm.eps must be positive, got {self.norm_eps!r}")
         if self.loop_times < 1:
             raise ConfigError("loop.times must be at least 1")
-        if self.loop_times > 1 and not 0 <= self.loop_start < self.loop_stop <= len(self.layers):
+        if self.loop_times > 1 and not 0 <= self.loop_start <= self.loop_stop <= len(self.layers):
             raise ConfigError(f"loop {self.loop_start}..{self.loop_stop} does not fit {len(self.layers)} layers")
 
     @classmethod
@@ -185,7 +185,7 @@ class LogesunConfig:
         """``(layer, embedding added right before it)`` for every layer run: the looped layers
         appear ``loop_times`` times, and every pass but the first starts from x + embedding."""
         n = len(self.layers)
-        if self.loop_times <= 1:
+        if self.loop_times <= 1 or self.loop_start >= self.loop_stop:  # nothing is repeated
             return [(i, False) for i in range(n)]
         order = [(i, False) for i in range(self.loop_start)]
         for rep in range(self.loop_times):

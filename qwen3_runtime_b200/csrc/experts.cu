@@ -31,12 +31,12 @@ constexpr int ROUTE_TT = 8;
 template <typename T>
 __global__ void __launch_bounds__(256)
 route_logits_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ router, int num_tokens, int E,
-                    int W, float* __restrict__ logits) {
-  extern __shared__ float route_rows[];  // [ROUTE_TT][W]
+                    int W, int tt, float* __restrict__ logits) {
+  extern __shared__ float route_rows[];  // [tt][W], tt <= ROUTE_TT tokens per block
   pdl_wait();
   pdl_launch_dependents();
-  const int t0 = blockIdx.x * ROUTE_TT;
-  const int nt = min(ROUTE_TT, num_tokens - t0);
+  const int t0 = blockIdx.x * tt;
+  const int nt = min(tt, num_tokens - t0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < nt * W; i += 256) {
     const int t = i / W, k = i - t * W;
@@ -124,20 +124,22 @@ Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float*
                            cudaStream_t stream) {
   if (!h || !router || !logits || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
-  const size_t smem = (size_t)ROUTE_TT * W * sizeof(float);
+  int tt = ROUTE_TT;  // fewer tokens per block when their rows would not fit in shared memory
+  while (tt > 1 && (size_t)tt * W * sizeof(float) > 128 * 1024) tt >>= 1;
+  const size_t smem = (size_t)tt * W * sizeof(float);
   if (smem > 200 * 1024 || (reinterpret_cast<uintptr_t>(router) & 15) || (E + 7) / 8 > 65535) return Q3_ERR_UNSUPPORTED;
-  const dim3 grid((num_tokens + ROUTE_TT - 1) / ROUTE_TT, (E + 7) / 8);
+  const dim3 grid((num_tokens + tt - 1) / tt, (E + 7) / 8);
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(route_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     e = launch_pdl(route_logits_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, h_stride, router,
-                   num_tokens, E, W, logits);
+                   num_tokens, E, W, tt, logits);
   } else if (dtype == Q3_DTYPE_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(route_logits_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     e = launch_pdl(route_logits_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)h, h_stride, router,
-                   num_tokens, E, W, logits);
+                   num_tokens, E, W, tt, logits);
   } else {
     return Q3_ERR_ARGUMENT;
   }

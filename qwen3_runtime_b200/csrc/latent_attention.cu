@@ -149,7 +149,7 @@ Q3_EXPORT int q3_rotate_heads(int dtype, const void* x, long xs_t, long xs_h, vo
 // exact expf.  A sink starts the running maximum at sink_h with a denominator of 1 and no value.
 // The order of every reduction depends on (p, window) only, so a token's result does not depend on
 // how the sequence was cut into steps or on what else is in the batch.
-constexpr int LATENT_MAX_ACC = 16;  // value width up to 32 * 16
+constexpr int LATENT_MAX_ACC = 32;  // value width up to 32 * 32
 
 template <typename T, int WARPS>
 __global__ void latent_attention_kernel(const T* __restrict__ q, long qs_t, long qs_h, const T* __restrict__ pages,

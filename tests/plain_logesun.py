@@ -11,8 +11,6 @@ the model.
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -114,7 +112,7 @@ def run_order(cfg: dict) -> list[tuple[int, bool]]:
     """(layer, whether the embedding output is added right before it) for every layer run."""
     n = len(cfg["layers"])
     loop = cfg.get("loop")
-    if not loop or loop.get("times", 1) <= 1:
+    if not loop or loop.get("times", 1) <= 1 or loop["start"] >= loop["stop"]:
         return [(i, False) for i in range(n)]
     start, stop, times = loop["start"], loop["stop"], loop["times"]
     order = [(i, False) for i in range(start)]
@@ -154,7 +152,3 @@ def forward(tokens: list[int], t: dict, cfg: dict, act=torch.float32, want_layer
     h = rms_norm(x, t["final.norm"], eps).to(act)
     logits = h.float() @ t["head"].to(act).float().t()
     return (logits, torch.stack(layers)) if want_layers else logits
-
-
-def default_scale(m: dict) -> float:
-    return 1.0 / math.sqrt(m["dim"] + m["rot_dim"])
