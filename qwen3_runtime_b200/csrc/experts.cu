@@ -389,18 +389,23 @@ Q3_EXPORT int q3_expert_down(int dtype, const void* mid, const void* down, void*
 // A block owns BM slots of one expert and 64 output columns (of gate and of up for GATE_UP); four
 // warps, WM = BM / 32 of them along the slots.  The slots' rows are gathered (and, for GATE_UP with
 // the weight on the input, multiplied by it and rounded to bfloat16) into shared memory, the
-// expert's rows come by cp.async, 32 of the inner dimension at a time.  K is a multiple of 8 and
-// all rows are 16-byte aligned.
+// expert's rows come by cp.async through a ring of three stages, 32 of the inner dimension at a
+// time, while the slots' rows of the step after next are already in registers.  K is a multiple of 8
+// and all rows are 16-byte aligned.
 template <bool GATE_UP, int BM>
 __global__ void __launch_bounds__(128)
 expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __restrict__ B, bf16* __restrict__ C,
                       int N, int K, const int* __restrict__ offsets, const int* __restrict__ tile_offsets,
                       const int* __restrict__ order, const float* __restrict__ weights, int E, int top,
                       int scale_input, float limit, float alpha, float up_offset) {
-  constexpr int BN = 64, BK = 32, KS = BK + 8, NB = GATE_UP ? 2 : 1;
+  constexpr int BN = 64, BK = 32, KS = BK + 8, NB = GATE_UP ? 2 : 1, STAGES = 3;
   constexpr int WM = BM / 32, WN = 4 / WM, COLS = BN / WN, NTW = COLS / 8;
-  __shared__ __align__(16) bf16 As[BM][KS];
-  __shared__ __align__(16) bf16 Ws[NB][BN][KS];
+  constexpr int A_CHUNKS = BM * (BK / 8) / 128;  // 16-byte chunks of the slots' rows per thread and step
+  extern __shared__ __align__(16) unsigned char expert_smem[];
+  typedef bf16 (*WTile)[BN][KS];
+  typedef bf16 (*ATile)[KS];
+  bf16* w_base = reinterpret_cast<bf16*>(expert_smem);             // [STAGES][NB][BN][KS]
+  bf16* a_base = w_base + STAGES * NB * BN * KS;                   // [2][BM][KS]
   __shared__ int slot_of[BM];
   __shared__ float scale_of[BM];
   pdl_wait();
@@ -420,29 +425,33 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
   const int wm = warp / WN, wn = warp % WN;
   const int n0 = blockIdx.x * BN;
   const bf16* Be = B + (long)e * NB * N * K;
-  float acc[NB][2][NTW][4];
-#pragma unroll
-  for (int b = 0; b < NB; ++b)
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < NTW; ++nt)
-#pragma unroll
-        for (int x = 0; x < 4; ++x) acc[b][mt][nt][x] = 0.f;
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    for (int c = tid; c < NB * BN * (BK / 8); c += 128) {
-      const int b = c / (BN * (BK / 8)), y = c % (BN * (BK / 8));
-      const int r = y / (BK / 8), ch = y % (BK / 8);
-      const int gn = n0 + r, gk = k0 + ch * 8;
-      const bool in = gn < N && gk < K;
-      cp_async16(smem_u32(&Ws[b][r][ch * 8]), in ? Be + ((long)b * N + gn) * K + gk : Be, in ? 16 : 0);
+  const int steps = (K + BK - 1) / BK;
+
+  // the expert's rows of step s into ring stage s % STAGES (one commit group per call, also when empty)
+  auto load_w = [&](int s) {
+    if (s < steps) {
+      WTile Ws = reinterpret_cast<WTile>(w_base + (s % STAGES) * NB * BN * KS);
+      const int k0 = s * BK;
+      for (int c = tid; c < NB * BN * (BK / 8); c += 128) {
+        const int b = c / (BN * (BK / 8)), y = c % (BN * (BK / 8));
+        const int r = y / (BK / 8), ch = y % (BK / 8);
+        const int gn = n0 + r, gk = k0 + ch * 8;
+        const bool in = gn < N && gk < K;
+        cp_async16(smem_u32(&Ws[b][r][ch * 8]), in ? Be + ((long)b * N + gn) * K + gk : Be, in ? 16 : 0);
+      }
     }
     cp_async_commit();
-    for (int c = tid; c < BM * (BK / 8); c += 128) {
+  };
+  // the slots' rows of step s into registers (gathered, and scaled where the weight is on the input)
+  uint4 a_regs[A_CHUNKS];
+  auto fetch_a = [&](int s) {
+#pragma unroll
+    for (int i = 0; i < A_CHUNKS; ++i) {
+      const int c = tid + i * 128;
       const int r = c / (BK / 8), ch = c % (BK / 8);
-      const int slot = slot_of[r], gk = k0 + ch * 8;
+      const int slot = slot_of[r], gk = s * BK + ch * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (slot >= 0 && gk < K) {
+      if (s < steps && slot >= 0 && gk < K) {
         const long arow = GATE_UP ? slot / top : slot;
         v = *reinterpret_cast<const uint4*>(A + arow * a_stride + gk);
         if (GATE_UP && scale_input) {
@@ -455,10 +464,40 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
           }
         }
       }
-      *reinterpret_cast<uint4*>(&As[r][ch * 8]) = v;
+      a_regs[i] = v;
     }
-    cp_async_wait<0>();
-    __syncthreads();
+  };
+  auto store_a = [&](int s) {
+    ATile As = reinterpret_cast<ATile>(a_base + (s & 1) * BM * KS);
+#pragma unroll
+    for (int i = 0; i < A_CHUNKS; ++i) {
+      const int c = tid + i * 128;
+      *reinterpret_cast<uint4*>(&As[c / (BK / 8)][(c % (BK / 8)) * 8]) = a_regs[i];
+    }
+  };
+
+  float acc[NB][2][NTW][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[b][mt][nt][x] = 0.f;
+  load_w(0);
+  load_w(1);
+  fetch_a(0);
+  store_a(0);
+  fetch_a(1);
+  for (int s = 0; s < steps; ++s) {
+    cp_async_wait<1>();  // the weights of step s have landed (those of s + 1 may still be on their way)
+    __syncthreads();     // ... for every thread; rows of step s are stored; step s - 1 has been used up
+    load_w(s + 2);       // into the stage step s - 1 used
+    store_a(s + 1);      // into the buffer step s - 1 used
+    fetch_a(s + 2);
+    WTile Ws = reinterpret_cast<WTile>(w_base + (s % STAGES) * NB * BN * KS);
+    ATile As = reinterpret_cast<ATile>(a_base + (s & 1) * BM * KS);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t a[2][4];
@@ -478,8 +517,8 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
           }
         }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -503,6 +542,11 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
     }
 }
 
+template <bool GATE_UP, int BM>
+static constexpr size_t expert_tc_smem() {
+  return (size_t)(3 * (GATE_UP ? 2 : 1) * 64 * 40 + 2 * BM * 40) * sizeof(bf16);
+}
+
 // The two products as above for bfloat16 with rows of 16-byte multiples; bm (32 or 64) is the row
 // tile that group_slots was given.
 Q3_EXPORT int q3_expert_gate_up_tc(const void* h, long h_stride, const void* gate_up, void* mid, int S, int E, int F,
@@ -518,7 +562,8 @@ Q3_EXPORT int q3_expert_gate_up_tc(const void* h, long h_stride, const void* gat
   if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
   const dim3 grid((F + 63) / 64, tiles);
   auto kernel = bm == 64 ? expert_gemm_tc_kernel<true, 64> : expert_gemm_tc_kernel<true, 32>;
-  return launch_pdl(kernel, grid, dim3(128), 0, stream, (const bf16*)h, h_stride, (const bf16*)gate_up, (bf16*)mid, F,
+  const size_t smem = bm == 64 ? expert_tc_smem<true, 64>() : expert_tc_smem<true, 32>();
+  return launch_pdl(kernel, grid, dim3(128), smem, stream, (const bf16*)h, h_stride, (const bf16*)gate_up, (bf16*)mid, F,
                     W, offsets, tile_offsets, order, weights, E, top, scale_input, limit, alpha, up_offset) == cudaSuccess
              ? Q3_OK
              : Q3_ERR_LAUNCH;
@@ -535,7 +580,8 @@ Q3_EXPORT int q3_expert_down_tc(const void* mid, const void* down, void* y, int 
   if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
   const dim3 grid((W + 63) / 64, tiles);
   auto kernel = bm == 64 ? expert_gemm_tc_kernel<false, 64> : expert_gemm_tc_kernel<false, 32>;
-  return launch_pdl(kernel, grid, dim3(128), 0, stream, (const bf16*)mid, (long)F, (const bf16*)down, (bf16*)y, W, F,
+  const size_t smem = bm == 64 ? expert_tc_smem<false, 64>() : expert_tc_smem<false, 32>();
+  return launch_pdl(kernel, grid, dim3(128), smem, stream, (const bf16*)mid, (long)F, (const bf16*)down, (bf16*)y, W, F,
                     offsets, tile_offsets, order, (const float*)nullptr, E, 1, 0, 0.f, 0.f, 0.f) == cudaSuccess
              ? Q3_OK
              : Q3_ERR_LAUNCH;

@@ -92,20 +92,20 @@ latent_attention_tc_kernel(const bf16* __restrict__ q, long qs_t, long qs_h, con
 
   // one tile of keys into a buffer: rows beyond the block's last key, and rows of released pages, as zeros
   auto load_tile = [&](int j0, bf16* dst) {
-    for (int c = tid; c < LTC_BN * chunks; c += LTC_THREADS) {
-      const int jj = c / chunks, ch = c - jj * chunks;
-      const int j = j0 + jj;
-      const bf16* src = pages;
-      int bytes = 0;
-      if (j <= j_hi) {
-        const int page = bt[j / ps];
-        if (page >= 0) {
-          src = pages + ((long)page * ps + (j % ps)) * dk + ch * 8;
-          bytes = 16;
-        }
+    // four threads per key row: one page lookup a thread, then 16-byte chunks four apart
+    const int jj = tid >> 2, j = j0 + jj;
+    const bf16* src = pages;
+    int bytes = 0;
+    if (j <= j_hi) {
+      const int page = bt[j / ps];
+      if (page >= 0) {
+        src = pages + ((long)page * ps + (j % ps)) * dk;
+        bytes = 16;
       }
-      cp_async16(smem_u32(dst + jj * kstride + ch * 8), src, bytes);  // 0 bytes: the chunk is zero-filled
     }
+    const uint32_t drow = smem_u32(dst + jj * kstride);
+    for (int ch = tid & 3; ch < chunks; ch += 4)
+      cp_async16(drow + ch * 16, bytes ? src + ch * 8 : src, bytes);  // 0 bytes: the chunk is zero-filled
     cp_async_commit();
   };
   // With two buffers the next tile is on its way while this one is worked on.
@@ -126,22 +126,39 @@ latent_attention_tc_kernel(const bf16* __restrict__ q, long qs_t, long qs_h, con
 
     // 1. scores of 16 keys for this warp's 16 rows
     {
-      float sc[2][4];
+      float sc[2][4], sd[2][4];  // even and odd steps of the reduction: two chains of dependent MMAs
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+        for (int e = 0; e < 4; ++e) sc[nt][e] = sd[nt][e] = 0.f;
       const int key0 = (warp & 3) * 16;
       const int a_row = mt * 16 + (lane & 15), a_col = (lane >> 4) * 8;
       const int b_row = key0 + ((lane >> 4) * 8) + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
-#pragma unroll 4
-      for (int k0 = 0; k0 < dk; k0 += 16) {
-        uint32_t a[4], bb[4];
-        ldmatrix_x4(a, smem_u32(Qs + a_row * kstride + k0 + a_col));
-        ldmatrix_x4(bb, smem_u32(Ks + b_row * kstride + k0 + b_col));
-        mma_bf16(sc[0], a, bb[0], bb[1]);
-        mma_bf16(sc[1], a, bb[2], bb[3]);
+      const uint32_t a_addr = smem_u32(Qs + a_row * kstride + a_col), b_addr = smem_u32(Ks + b_row * kstride + b_col);
+      int k0 = 0;
+#pragma unroll 2
+      for (; k0 + 32 <= dk; k0 += 32) {
+        uint32_t a0[4], b0[4], a1[4], b1[4];
+        ldmatrix_x4(a0, a_addr + k0 * 2);
+        ldmatrix_x4(b0, b_addr + k0 * 2);
+        ldmatrix_x4(a1, a_addr + k0 * 2 + 32);
+        ldmatrix_x4(b1, b_addr + k0 * 2 + 32);
+        mma_bf16(sc[0], a0, b0[0], b0[1]);
+        mma_bf16(sc[1], a0, b0[2], b0[3]);
+        mma_bf16(sd[0], a1, b1[0], b1[1]);
+        mma_bf16(sd[1], a1, b1[2], b1[3]);
       }
+      if (k0 < dk) {  // dk is a multiple of 16: one step is left
+        uint32_t a0[4], b0[4];
+        ldmatrix_x4(a0, a_addr + k0 * 2);
+        ldmatrix_x4(b0, b_addr + k0 * 2);
+        mma_bf16(sc[0], a0, b0[0], b0[1]);
+        mma_bf16(sc[1], a0, b0[2], b0[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] += sd[nt][e];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const int r = mt * 16 + (lane >> 2), cidx = key0 + nt * 8 + 2 * (lane & 3);
