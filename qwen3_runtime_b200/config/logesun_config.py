@@ -37,7 +37,7 @@ class LatentAttentionConfig:
     scale: float
     rot_dims: int  # how many of the rotated part's dimensions turn (pairs 2i, 2i + 1)
     rot_base: float
-    window: int | None  # a query sees itself and the window - 1 tokens before it; None: all
+    window: int | None  # the query at position p reads positions max(0, p - window + 1) .. p; None: all from 0
 
     @classmethod
     def from_raw(cls, where: str, raw: Mapping[str, Any]) -> "LatentAttentionConfig":

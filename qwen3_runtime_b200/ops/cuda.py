@@ -425,8 +425,8 @@ class CudaOps:
         """Causal attention of every token over its sequence's cached rows, all heads sharing them:
         ``q`` ``[T, H, width]`` already in the rows' space, ``pages`` ``[pages, page_size, width]``, the
         value of a row its first ``value_dim`` elements, ``out`` ``[T, H, value_dim]``.  ``sink``
-        (float32 ``[H]`` or None) joins the softmax denominator; ``window``: a query sees itself and the
-        ``window - 1`` rows before it."""
+        (float32 ``[H]`` or None) joins the softmax denominator; ``window``: the query at position p
+        reads rows ``max(0, p - window + 1) .. p``."""
         T, H, width = q.shape
         if pages.shape[-1] != width or not pages.is_contiguous() or out.shape != (T, H, value_dim):
             raise KernelError("latent_attention: pages are dense [pages, page_size, width of q]")

@@ -9,9 +9,9 @@ Per token the cache keeps one row ``[c | k^rot]`` for all heads.  Keys and value
 expanded: since ``q^plain . (W_uk c) = (W_uk^T q^plain) . c`` the query is moved into the latent
 space (one small product per head), attention runs over the cached rows with all heads sharing
 them -- the value of a row is its first ``kv_rank`` elements -- and ``W_uv`` is applied to the
-attended latent.  Optional: a window (a query sees itself and the ``window - 1`` rows before it)
-and a learned sink per head (``exp(sink_h)`` is added to the softmax denominator; it has no key
-and no value and is not scaled).
+attended latent.  Optional: a window (the query at position p reads rows max(0, p - window + 1) .. p)
+and a learned sink per head: a logit that enters the softmax denominator as exp(sink_h), unscaled,
+with nothing to attend to behind it.
 """
 
 from __future__ import annotations

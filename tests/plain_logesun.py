@@ -41,9 +41,9 @@ def rotate_interleaved(x: torch.Tensor, positions: torch.Tensor, dims: int, base
 
 
 def window_sink_attention(q, k, v, scale: float, window: int | None, sink: torch.Tensor | None) -> torch.Tensor:
-    """``q, k`` ``[T, H, Dk]``, ``v`` ``[T, H, Dv]`` of one sequence from position 0.  Query i sees
-    keys j with 0 <= i - j < window; the softmax denominator also holds exp(sink_h), which has no
-    value."""
+    """``q, k`` ``[T, H, Dk]``, ``v`` ``[T, H, Dv]`` of one sequence from position 0.  The query at
+    position p reads keys max(0, p - window + 1) .. p; exp(sink_h) is one more term of the softmax
+    denominator and brings no value."""
     T, H, _ = q.shape
     scores = torch.einsum("ihd,jhd->hij", q.float(), k.float()) * scale
     i = torch.arange(T)[:, None]
