@@ -22,9 +22,26 @@ from .manager import GroupSpec
 
 @dataclass(frozen=True)
 class KVLayerSpec:
+    """``value_dim``: values have a size of their own (None: the keys' ``head_dim``); keys and values
+    are then two device tensors, ``[layers, pages + 1, kv_heads, page_size, head_dim | value_dim]``."""
+
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def split(self) -> bool:
+        return self.value_dim is not None and self.value_dim != self.head_dim
+
+
+def flatten_specs(spec) -> list:
+    """A mixer may need several cache layers at once (pages for keys and values beside a state slot,
+    two mixers side by side): its spec is then a tuple of specs, possibly nested.  The leaves in
+    order."""
+    if isinstance(spec, (tuple, list)):
+        return [leaf for part in spec for leaf in flatten_specs(part)]
+    return [spec]
 
 
 @dataclass(frozen=True)
@@ -47,17 +64,27 @@ class StateLayerSpec:
 class GroupLayout:
     spec: GroupSpec
     layer_spec: object  # KVLayerSpec | StateLayerSpec
-    cache_ids: tuple[int, ...]  # cache layers of this group, in order
+    cache_ids: tuple  # cache layers of this group, in order (ids, or (id, leaf) of a composite spec)
 
 
 class CacheLayout:
-    """Groups for a model: ``layer_specs`` maps cache layer id -> its spec (or None)."""
+    """Groups for a model: ``layer_specs`` maps cache layer id -> its spec (or None).  A spec that is
+    a tuple (see :func:`flatten_specs`) stands for several cache layers: leaf ``k`` of cache layer
+    ``c`` is kept under the id ``(c, k)``, and ``composite[c]`` is the tuple itself, so that the
+    storage can hand the mixer its views in the same arrangement."""
 
     def __init__(self, layer_specs: dict[int, object]):
-        buckets: dict[object, list[int]] = {}
+        buckets: dict[object, list] = {}
+        self.composite: dict[int, object] = {}
         for cache_id in sorted(layer_specs):
             spec = layer_specs[cache_id]
             if spec is None:
+                continue
+            if isinstance(spec, (tuple, list)):
+                self.composite[cache_id] = spec
+                for k, leaf in enumerate(flatten_specs(spec)):
+                    if leaf is not None:
+                        buckets.setdefault(leaf, []).append((cache_id, k))
                 continue
             buckets.setdefault(spec, []).append(cache_id)
         self.groups: list[GroupLayout] = []
@@ -91,7 +118,8 @@ class CacheLayout:
             if isinstance(s, LatentLayerSpec):
                 out.append(len(g.cache_ids) * s.width * page_size * dtype_bytes)
             else:
-                out.append(len(g.cache_ids) * 2 * s.num_kv_heads * s.head_dim * page_size * dtype_bytes)
+                per_token = s.num_kv_heads * (s.head_dim + (s.value_dim or s.head_dim))
+                out.append(len(g.cache_ids) * per_token * page_size * dtype_bytes)
         return out
 
     def token_bytes(self, dtype_bytes: int) -> int:

@@ -6,7 +6,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .layout import CacheLayout, KVLayerSpec, LatentLayerSpec, StateLayerSpec
+from .layout import CacheLayout, KVLayerSpec, LatentLayerSpec, StateLayerSpec, flatten_specs
 
 
 @dataclass
@@ -42,7 +42,12 @@ class CacheStorage:
         self.tensors: list[torch.Tensor] = []
         for gi, g in enumerate(layout.groups):
             s = g.layer_spec
-            if isinstance(s, KVLayerSpec):
+            if isinstance(s, KVLayerSpec) and s.split:  # keys and values of unlike sizes: a tensor each
+                pages = self.num_pages[layout.paged_groups.index(gi)]
+                shape = (len(g.cache_ids), pages + 1, s.num_kv_heads, page_size)
+                self.tensors.append((torch.zeros((*shape, s.head_dim), dtype=dtype, device=device),
+                                     torch.zeros((*shape, s.value_dim), dtype=dtype, device=device)))
+            elif isinstance(s, KVLayerSpec):
                 pages = self.num_pages[layout.paged_groups.index(gi)]
                 shape = (len(g.cache_ids), 2, pages + 1, s.num_kv_heads, page_size, s.head_dim)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
@@ -55,12 +60,26 @@ class CacheStorage:
                 shape = (len(g.cache_ids), num_slots + 1, *s.shape)
                 self.tensors.append(torch.zeros(shape, dtype=getattr(torch, s.dtype), device=device))
 
-    def view(self, cache_id: int, writes: bool = True) -> CacheLayerView | None:
+    def view(self, cache_id, writes: bool = True):
+        """What the mixer of one run entry sees: a :class:`CacheLayerView`, None (no cache), or, for a
+        mixer whose spec is a tuple of specs, views in the same (possibly nested) arrangement."""
+        if cache_id in self.layout.composite:
+            leaves = iter(range(len(flatten_specs(self.layout.composite[cache_id]))))
+
+            def arrange(spec):
+                if isinstance(spec, (tuple, list)):
+                    return tuple(arrange(part) for part in spec)
+                return self.view((cache_id, next(leaves)), writes)
+
+            return arrange(self.layout.composite[cache_id])
         if cache_id not in self.layout.where:
             return None
         gi, li = self.layout.where[cache_id]
         g = self.layout.groups[gi]
         t = self.tensors[gi]
+        if isinstance(t, tuple):
+            return CacheLayerView(gi, self.layout.paged_groups.index(gi), self.page_size, g.spec.window,
+                                  t[0][li], t[1][li], None, writes)
         if g.spec.paged and isinstance(g.layer_spec, LatentLayerSpec):
             return CacheLayerView(gi, self.layout.paged_groups.index(gi), self.page_size, g.spec.window,
                                   None, None, None, writes, latent_pages=t[li])
@@ -85,10 +104,14 @@ class CacheStorage:
         """Overwrite pages (tests: a page that is used again must not leak old contents)."""
         gi = self.layout.paged_groups[paged_index]
         t = self.tensors[gi]
-        if pages and isinstance(self.layout.groups[gi].layer_spec, LatentLayerSpec):
+        if pages and isinstance(t, tuple):
+            for part in t:
+                part[:, torch.tensor(pages, dtype=torch.long, device=part.device)] = value
+        elif pages and isinstance(self.layout.groups[gi].layer_spec, LatentLayerSpec):
             t[:, torch.tensor(pages, dtype=torch.long, device=t.device)] = value
         elif pages:
             t[:, :, torch.tensor(pages, dtype=torch.long, device=t.device)] = value
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.tensors)
+        flat = [x for t in self.tensors for x in (t if isinstance(t, tuple) else (t,))]
+        return sum(t.numel() * t.element_size() for t in flat)

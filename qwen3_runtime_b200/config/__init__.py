@@ -1,5 +1,6 @@
 from .engine_config import EngineConfig, canonical_dtype
 from .logesun_config import LogesunConfig
+from .puladra_config import PuladraConfig
 from .model_config import ConfigError, Qwen3Config
 from .registry import (
     Architecture,
@@ -24,6 +25,7 @@ __all__ = [
     "LogesunConfig",
     "ModelSpec",
     "PartSpec",
+    "PuladraConfig",
     "Qwen3Config",
     "canonical_dtype",
     "load_config",

@@ -37,13 +37,17 @@ class LayerRun:
     whether this entry stores its own keys/values (or state) there or only reads
     what an earlier entry stored.  ``add_embedding``: the embedding output (the
     residual stream as it was before the first entry) is added to the stream right
-    before this entry runs (a looped stack that is fed its input again).
+    before this entry runs (a looped stack that is fed its input again).  ``add_row``
+    ``(table, row)``: row ``row`` of the model's shared table ``table`` (``ModelSpec.shared_tables``),
+    one vector of the model's width, is added to every token of the stream right before this
+    entry runs (a learned vector per pass of a loop).
     """
 
     block: int
     cache: int
     writes: bool = True
     add_embedding: bool = False
+    add_row: tuple[str, int] | None = None
 
 
 @dataclass(frozen=True)
@@ -61,6 +65,10 @@ class ModelSpec:
     # the head's epilogue: logits * logit_scale, then (if set) softcap * tanh(logits / softcap)
     logit_scale: float = 1.0
     logit_softcap: float | None = None
+    # stored tensors that belong to no block: checkpoint name -> (shape, kind as in ParamSpec).  The
+    # model loads them into ``BuildContext.shared`` under their names, where parts (a second embedding
+    # that every block reads a slice of) and run entries (``LayerRun.add_row``) find them.
+    shared_tables: tuple[tuple[str, tuple[int, ...], str], ...] = ()
 
     def __post_init__(self) -> None:
         if self.logit_softcap is not None and not self.logit_softcap > 0:
@@ -75,6 +83,8 @@ class ModelSpec:
                 writers.add(run.cache)
             elif run.cache not in writers:
                 raise ValueError(f"run entry reads cache layer {run.cache} before any entry writes it")
+            if run.add_row is not None and run.add_row[0] not in {name for name, _s, _k in self.shared_tables}:
+                raise ValueError(f"run entry adds a row of {run.add_row[0]!r}, which is no shared table of the model")
 
     @staticmethod
     def sequential_order(num_blocks: int) -> tuple[LayerRun, ...]:

@@ -1,7 +1,7 @@
 // Causal attention over the paged cache for any mix of prompt portions and single
 // decoded tokens: the general kernel (any head_dim that is a multiple of 8 up to
-// 256, any head counts, any page size, optional window), used by the fp32 path and
-// wherever a specialised kernel refuses a size.
+// 256, a value size of its own up to 256, any head counts, any page size, optional
+// window), used by the fp32 path and wherever a specialised kernel refuses a size.
 //
 // One warp per (token, query head).  The query at absolute position p attends to
 // keys lo..p of its own sequence (lo = p - window + 1 with a window, else 0), which
@@ -19,7 +19,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
                                                const int* __restrict__ block_table, int max_pages,
                                                const int* __restrict__ token_seq,
                                                const int* __restrict__ positions, T* __restrict__ out,
-                                               int num_tokens, int nq, int nkv, int D, int ps, float scale,
+                                               long out_stride, int num_tokens, int nq, int nkv, int D, int Dv, int ps, float scale,
                                                int window) {
   extern __shared__ float qs_all[];  // WARPS * D
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -42,12 +42,12 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
   for (int j0 = lo & ~31; j0 <= p; j0 += 32) {
     const int j = j0 + lane;
     const bool valid = j >= lo && j <= p;
-    long row = 0;
+    long row = 0;  // the key's row among all (page, head, place) rows; keys have D, values Dv elements
     float s = -INFINITY;
     if (valid) {
       const int page = bt[j / ps];
-      row = (((long)page * nkv + kvh) * ps + (j % ps)) * D;
-      const T* kr = kpages + row;
+      row = ((long)page * nkv + kvh) * ps + (j % ps);
+      const T* kr = kpages + row * D;
       float dot = 0.f;
       for (int d = 0; d < D; d += 8) {
         float kv[8];
@@ -68,34 +68,36 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
       const float pj = __shfl_sync(0xffffffffu, pl, jj);
       const long rj = __shfl_sync(0xffffffffu, row, jj);
       if (pj == 0.f) continue;  // keys before the window, or fully underflowed
-      const T* vr = vpages + rj;
+      const T* vr = vpages + rj * Dv;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const int d = lane + 32 * c;
-        if (d < D) acc[c] = fmaf(pj, to_f32(vr[d]), acc[c]);
+        if (d < Dv) acc[c] = fmaf(pj, to_f32(vr[d]), acc[c]);
       }
     }
     m = m_new;
   }
-  T* orow = out + ((long)t * nq + h) * D;
+  T* orow = out + (long)t * out_stride + (long)h * Dv;
   const float inv = 1.f / l;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const int d = lane + 32 * c;
-    if (d < D) orow[d] = from_f32<T>(acc[c] * inv);
+    if (d < Dv) orow[d] = from_f32<T>(acc[c] * inv);
   }
 }
 
-// q: [num_tokens, *] with row stride q_stride (elements), head h at column h*D.
-// out: [num_tokens, nq*D].  window <= 0: none.
+// q: [num_tokens, *] with row stride q_stride (elements), head h at column h*D.  Keys are
+// [pages, nkv, ps, D], values [pages, nkv, ps, Dv].  out: rows out_stride elements apart, head h at
+// column h*Dv.  window <= 0: none.
 Q3_EXPORT int q3_paged_attention_generic(int dtype, const void* q, int q_stride, const void* kpages,
                                          const void* vpages, const int* block_table, int max_pages,
                                          const int* token_seq, const int* positions, void* out,
-                                         int num_tokens, int nq, int nkv, int D, int ps, float scale,
+                                         long out_stride, int num_tokens, int nq, int nkv, int D, int Dv, int ps,
+                                         float scale,
                                          int window, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !token_seq || !positions || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1) return Q3_ERR_ARGUMENT;
-  if (D < 8 || D % 8 || D > 256) return Q3_ERR_UNSUPPORTED;
+  if (D < 8 || D % 8 || D > 256 || Dv < 1 || Dv > 256 || out_stride < (long)nq * Dv) return Q3_ERR_UNSUPPORTED;
   if (num_tokens == 0) return Q3_OK;
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * D * sizeof(float);
@@ -104,11 +106,11 @@ Q3_EXPORT int q3_paged_attention_generic(int dtype, const void* q, int q_stride,
   if (dtype == Q3_DTYPE_F32)
     paged_attention_generic_kernel<float, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (const float*)q, q_stride, (const float*)kpages, (const float*)vpages, block_table, max_pages,
-        token_seq, positions, (float*)out, num_tokens, nq, nkv, D, ps, scale, window);
+        token_seq, positions, (float*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window);
   else if (dtype == Q3_DTYPE_BF16)
     paged_attention_generic_kernel<bf16, WARPS><<<blocks, WARPS * 32, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)kpages, (const bf16*)vpages, block_table, max_pages,
-        token_seq, positions, (bf16*)out, num_tokens, nq, nkv, D, ps, scale, window);
+        token_seq, positions, (bf16*)out, out_stride, num_tokens, nq, nkv, D, Dv, ps, scale, window);
   else
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();

@@ -78,14 +78,16 @@ route_logits_kernel(const T* __restrict__ h, long h_stride, const float* __restr
   }
 }
 
-__global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, int E, int top, int renormalize,
+// mode 0: weights are the chosen logits' sigmoids; 1: those divided by their sum; 2: the softmax over
+// the chosen logits only.
+__global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, int E, int top, int mode,
                                   int* __restrict__ chosen, float* __restrict__ weights) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= num_tokens) return;
   float* z = logits + (long)t * E;
-  float total = 0.f;
+  float total = 0.f, first = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -105,7 +107,8 @@ __global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, in
         at = oa;
       }
     }
-    const float score = 1.f / (1.f + expf(-best));
+    if (k == 0) first = best;  // the largest logit: the softmax's reference point
+    const float score = mode == 2 ? expf(best - first) : 1.f / (1.f + expf(-best));
     if (lane == 0) {
       chosen[(long)t * top + k] = at;
       weights[(long)t * top + k] = score;
@@ -114,13 +117,13 @@ __global__ void route_pick_kernel(float* __restrict__ logits, int num_tokens, in
     total += score;
     __syncwarp();
   }
-  if (renormalize)
+  if (mode)
     for (int k = lane; k < top; k += 32) weights[(long)t * top + k] /= total;
 }
 
 // logits: fp32 scratch [num_tokens, E] (left with the chosen entries at -inf).
 Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float* router, int num_tokens, int E, int W,
-                           int top, int renormalize, float* logits, int* chosen, float* weights,
+                           int top, int mode, float* logits, int* chosen, float* weights,
                            cudaStream_t stream) {
   if (!h || !router || !logits || !chosen || !weights || E < 1 || W < 1 || top < 1 || top > E) return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
@@ -145,7 +148,7 @@ Q3_EXPORT int q3_route_top(int dtype, const void* h, long h_stride, const float*
   }
   if (e != cudaSuccess) return Q3_ERR_LAUNCH;
   e = launch_pdl(route_pick_kernel, dim3((num_tokens + 3) / 4), dim3(128), 0, stream, logits, num_tokens, E, top,
-                 renormalize, chosen, weights);
+                 mode, chosen, weights);
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
@@ -242,8 +245,10 @@ __device__ __forceinline__ int expert_of_tile(const int* __restrict__ tile_offse
 }
 
 // GATE_UP: A rows are h[token(slot)] (times the slot's weight when scale_input), B is the expert's
-// [2F, W] (gate rows, then up rows), the result mid[slot, F].  Else: A rows are mid[slot], B is the
-// expert's [W, F], the result y[slot, W].
+// [2F, W] (gate rows, then up rows), the result mid[slot, F].  Else: A rows are A[slot / top] (top = 1:
+// a row per slot, the second product; top = the choices per token: the token's row, a first product
+// without a gate), B is the expert's [N, K], the result C[slot, N]; scale_input then stands for the
+// activation: 0 none, 1 the squared ReLU of the rounded product.
 template <typename T, bool GATE_UP>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(const T* __restrict__ A, long a_stride, const T* __restrict__ B, T* __restrict__ C, int N, int K,
@@ -286,7 +291,7 @@ expert_gemm_kernel(const T* __restrict__ A, long a_stride, const T* __restrict__
       const int slot = slot_of[r], gk = k0 + c;
       float a = 0.f;
       if (slot >= 0 && gk < K) {
-        const long arow = GATE_UP ? slot / top : slot;
+        const long arow = slot / top;
         a = to_f32(A[arow * a_stride + gk]);
         if (GATE_UP && scale_input) a = to_f32(from_f32<T>(a * scale_of[r]));
       }
@@ -331,6 +336,9 @@ expert_gemm_kernel(const T* __restrict__ A, long a_stride, const T* __restrict__
         const float g = fminf(to_f32(from_f32<T>(acc[0][i][j])), limit);
         const float u = fminf(fmaxf(to_f32(from_f32<T>(acc[NB - 1][i][j])), -limit), limit);
         C[(long)slot * N + gn] = from_f32<T>((g / (1.f + expf(-alpha * g))) * (u + up_offset));
+      } else if (scale_input) {
+        const float r = fmaxf(to_f32(from_f32<T>(acc[0][i][j])), 0.f);
+        C[(long)slot * N + gn] = from_f32<T>(r * r);
       } else {
         C[(long)slot * N + gn] = from_f32<T>(acc[0][i][j]);
       }
@@ -380,6 +388,31 @@ Q3_EXPORT int q3_expert_down(int dtype, const void* mid, const void* down, void*
     e = launch_pdl(expert_gemm_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16*)mid, (long)F,
                    (const bf16*)down, (bf16*)y, W, F, offsets, tile_offsets, order, (const float*)nullptr, E, 1, 0, 0.f,
                    0.f, 0.f);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// An expert's first product without a gate: mid[slot] = act(W_up_e h[token(slot)]); up: [E, F, W].
+// act 1: the squared ReLU.
+Q3_EXPORT int q3_expert_up(int dtype, const void* h, long h_stride, const void* up, void* mid, int S, int E, int F,
+                           int W, int top, const int* offsets, const int* tile_offsets, const int* order, int act,
+                           cudaStream_t stream) {
+  if (!h || !up || !mid || !offsets || !tile_offsets || !order || E < 1 || F < 1 || W < 1 || top < 1)
+    return Q3_ERR_ARGUMENT;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / EXPERT_BM + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((F + 63) / 64, tiles);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(expert_gemm_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)h, h_stride,
+                   (const float*)up, (float*)mid, F, W, offsets, tile_offsets, order, (const float*)nullptr, E, top,
+                   act, 0.f, 0.f, 0.f);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(expert_gemm_kernel<bf16, false>, grid, dim3(256), 0, stream, (const bf16*)h, h_stride,
+                   (const bf16*)up, (bf16*)mid, F, W, offsets, tile_offsets, order, (const float*)nullptr, E, top, act,
+                   0.f, 0.f, 0.f);
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
@@ -452,7 +485,7 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
       const int slot = slot_of[r], gk = s * BK + ch * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (s < steps && slot >= 0 && gk < K) {
-        const long arow = GATE_UP ? slot / top : slot;
+        const long arow = slot / top;
         v = *reinterpret_cast<const uint4*>(A + arow * a_stride + gk);
         if (GATE_UP && scale_input) {
           __nv_bfloat162* hv = reinterpret_cast<__nv_bfloat162*>(&v);
@@ -535,6 +568,9 @@ expert_gemm_tc_kernel(const bf16* __restrict__ A, long a_stride, const bf16* __r
             const float g = fminf(to_f32(from_f32<bf16>(acc[0][mt][nt][2 * half + x])), limit);
             const float u = fminf(fmaxf(to_f32(from_f32<bf16>(acc[NB - 1][mt][nt][2 * half + x])), -limit), limit);
             C[(long)slot * N + gn] = from_f32<bf16>((g / (1.f + expf(-alpha * g))) * (u + up_offset));
+          } else if (scale_input) {
+            const float r = fmaxf(to_f32(from_f32<bf16>(acc[0][mt][nt][2 * half + x])), 0.f);
+            C[(long)slot * N + gn] = from_f32<bf16>(r * r);
           } else {
             C[(long)slot * N + gn] = from_f32<bf16>(acc[0][mt][nt][2 * half + x]);
           }
@@ -587,10 +623,31 @@ Q3_EXPORT int q3_expert_down_tc(const void* mid, const void* down, void* y, int 
              : Q3_ERR_LAUNCH;
 }
 
+Q3_EXPORT int q3_expert_up_tc(const void* h, long h_stride, const void* up, void* mid, int S, int E, int F, int W,
+                              int top, int bm, const int* offsets, const int* tile_offsets, const int* order, int act,
+                              cudaStream_t stream) {
+  if (!h || !up || !mid || !offsets || !tile_offsets || !order || E < 1 || F < 1 || W < 1 || top < 1)
+    return Q3_ERR_ARGUMENT;
+  if (bm != 32 && bm != 64) return Q3_ERR_ARGUMENT;
+  if (W % 8 || h_stride % 8 || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(up) & 15))
+    return Q3_ERR_UNSUPPORTED;
+  if (S == 0) return Q3_OK;
+  const int tiles = S / bm + (E < S ? E : S);
+  if (tiles > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid((F + 63) / 64, tiles);
+  auto kernel = bm == 64 ? expert_gemm_tc_kernel<false, 64> : expert_gemm_tc_kernel<false, 32>;
+  const size_t smem = bm == 64 ? expert_tc_smem<false, 64>() : expert_tc_smem<false, 32>();
+  return launch_pdl(kernel, grid, dim3(128), smem, stream, (const bf16*)h, h_stride, (const bf16*)up, (bf16*)mid, F, W,
+                    offsets, tile_offsets, order, (const float*)nullptr, E, top, act, 0.f, 0.f, 0.f) == cudaSuccess
+             ? Q3_OK
+             : Q3_ERR_LAUNCH;
+}
+
 // ---- per-token sum ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weights, const T* __restrict__ shared,
-                               T* __restrict__ out, long total, int W, int top) {
+                               const T* __restrict__ shared_gate, long gate_stride, T* __restrict__ out, long total,
+                               int W, int top) {
   pdl_wait();
   pdl_launch_dependents();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -602,14 +659,19 @@ __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict_
     const float v = to_f32(y[(t * top + k) * W + i]);
     sum += weights ? v * weights[t * top + k] : v;
   }
-  if (shared) sum += to_f32(shared[idx]);
+  if (shared) {
+    const float v = to_f32(shared[idx]);
+    sum += shared_gate ? v / (1.f + expf(-to_f32(shared_gate[t * gate_stride]))) : v;
+  }
   out[idx] = from_f32<T>(sum);
 }
 
 // y: [T * top, W]; weights: fp32 [T * top] or null (the weight was applied to the input);
-// shared: [T, W] or null; out: [T, W].
-Q3_EXPORT int q3_expert_combine(int dtype, const void* y, const float* weights, const void* shared, void* out,
-                                int num_tokens, int W, int top, cudaStream_t stream) {
+// shared: [T, W] or null; shared_gate: one logit per token, gate_stride elements apart, or null: the
+// shared expert's result is multiplied by the logit's sigmoid; out: [T, W].
+Q3_EXPORT int q3_expert_combine(int dtype, const void* y, const float* weights, const void* shared,
+                                const void* shared_gate, long gate_stride, void* out, int num_tokens, int W, int top,
+                                cudaStream_t stream) {
   if (!y || !out || W < 1 || top < 1) return Q3_ERR_ARGUMENT;
   const long total = (long)num_tokens * W;
   if (total == 0) return Q3_OK;
@@ -617,10 +679,10 @@ Q3_EXPORT int q3_expert_combine(int dtype, const void* y, const float* weights, 
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)y, weights,
-                   (const float*)shared, (float*)out, total, W, top);
+                   (const float*)shared, (const float*)shared_gate, gate_stride, (float*)out, total, W, top);
   else if (dtype == Q3_DTYPE_BF16)
     e = launch_pdl(combine_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)y, weights,
-                   (const bf16*)shared, (bf16*)out, total, W, top);
+                   (const bf16*)shared, (const bf16*)shared_gate, gate_stride, (bf16*)out, total, W, top);
   else
     return Q3_ERR_ARGUMENT;
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;

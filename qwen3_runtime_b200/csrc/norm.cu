@@ -294,13 +294,17 @@ Q3_EXPORT int q3_logit_scale_cap(float* logits, long total, float scale, float c
 //   y'  = post_w ? (y * rsqrt(mean(y^2) + post_eps)) * post_w : y
 //   v   = (ids ? table[ids[r]] : resid[r]) + y' + (add_ids ? add_table[add_ids[r]] : 0)
 //   resid[r] = v (when write_resid);   out[i] = (v * rsqrt(mean(v^2) + eps)) * w
-// `add_ids/add_table` add embedding rows to the sum once more (a looped stack fed its input again).
+// `add_ids/add_table` add embedding rows to the sum once more (a looped stack fed its input again);
+// `add_vec` (fp32 [H]) is added to every row's sum (a learned offset per pass of a loop).  Without `w`
+// nothing is normalised: out = v, rounded (the stream itself as the input of a product).
 // One block per row; the row's y and v stay in shared memory between the passes.
 template <typename T>
-__global__ void fused_post_norm_kernel(const T* __restrict__ pending, const float* __restrict__ post_w, float post_eps,
+__global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int parts, long part_stride,
+                                       const float* __restrict__ post_w, float post_eps,
                                        float* __restrict__ resid, const int* __restrict__ ids,
                                        const T* __restrict__ table, const int* __restrict__ add_ids,
-                                       const T* __restrict__ add_table, const int* __restrict__ rows,
+                                       const T* __restrict__ add_table, const float* __restrict__ add_vec,
+                                       const int* __restrict__ rows,
                                        const float* __restrict__ w, T* __restrict__ out, int H, float eps,
                                        int write_resid, int vocab) {
   extern __shared__ float vals[];  // y[H], v[H], 33 for the reductions
@@ -312,11 +316,19 @@ __global__ void fused_post_norm_kernel(const T* __restrict__ pending, const floa
   const int r = blockIdx.x;
   const long src = rows ? rows[r] : r;
   float post_rstd = 1.f;
+  const bool pending = pending_any != nullptr;
   if (pending) {
-    const T* prow = pending + src * H;
+    const T* prow = static_cast<const T*>(pending_any) + src * H;
+    const float* frow = static_cast<const float*>(pending_any) + src * H;  // with parts: fp32 planes, added in order
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      const float y = to_f32(prow[i]);
+      float y;
+      if (parts) {
+        y = frow[i];
+        for (int p = 1; p < parts; ++p) y += frow[p * part_stride + i];
+      } else {
+        y = to_f32(prow[i]);
+      }
       ys[i] = y;
       ss += y * y;
     }
@@ -340,20 +352,26 @@ __global__ void fused_post_norm_kernel(const T* __restrict__ pending, const floa
     float v = trow ? to_f32(trow[i]) : rrow[i];
     if (pending) v += post_w ? (ys[i] * post_rstd) * post_w[i] : ys[i];
     if (arow) v += to_f32(arow[i]);
+    if (add_vec) v += add_vec[i];
     if (write_resid) rrow[i] = v;
     vs[i] = v;
     ss += v * v;
   }
-  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
   T* orow = out + (long)r * H;
+  if (!w) {  // the sum itself, rounded to the output's type
+    for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>(vs[i]);
+    return;
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>((vs[i] * rstd) * w[i]);
 }
 
 template <typename T>
-static int launch_fused_post_norm(const void* pending, const float* post_w, float post_eps, float* resid,
+static int launch_fused_post_norm(const void* pending, int parts, long part_stride, const float* post_w, float post_eps,
+                                  float* resid,
                                   const int* ids, const void* table, const int* add_ids, const void* add_table,
-                                  const int* rows, const float* w, void* out, int num_rows, int H, float eps,
-                                  int write_resid, int vocab, cudaStream_t stream) {
+                                  const float* add_vec, const int* rows, const float* w, void* out, int num_rows,
+                                  int H, float eps, int write_resid, int vocab, cudaStream_t stream) {
   if (num_rows == 0) return Q3_OK;
   const size_t smem = (size_t)(2 * H + 33) * sizeof(float);
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
@@ -361,29 +379,32 @@ static int launch_fused_post_norm(const void* pending, const float* post_w, floa
     cudaFuncSetAttribute(fused_post_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   int threads = ((H / 4 + 31) / 32) * 32;  // about four elements a thread: the row's loads are all in flight at once
   threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
-  return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, (const T*)pending, post_w,
-                    post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, rows, w, (T*)out, H, eps,
-                    write_resid, vocab) == cudaSuccess
+  return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, pending, parts, part_stride,
+                    post_w, post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, add_vec, rows, w, (T*)out, H,
+                    eps, write_resid, vocab) == cudaSuccess
              ? Q3_OK
              : Q3_ERR_LAUNCH;
 }
 
-// pending, table, add_table and out have `dtype`; post_w and w are fp32 [H]; resid is fp32.
-Q3_EXPORT int q3_fused_post_norm(int dtype, const void* pending, const float* post_w, float post_eps, float* resid,
+// pending (pending_parts = 0), table, add_table and out have `dtype`; with pending_parts > 0 pending is
+// fp32 [pending_parts, rows, H], planes part_stride elements apart; post_w and w are fp32 [H]; resid is fp32.
+Q3_EXPORT int q3_fused_post_norm(int dtype, const void* pending, int pending_parts, long part_stride,
+                                 const float* post_w, float post_eps, float* resid,
                                  const int* ids, const void* table, const int* add_ids, const void* add_table,
-                                 const int* rows, const float* w, void* out, int num_rows, int H, float eps,
-                                 int write_resid, int vocab, cudaStream_t stream) {
-  if (!w || !out || H < 1) return Q3_ERR_ARGUMENT;
+                                 const float* add_vec, const int* rows, const float* w, void* out, int num_rows,
+                                 int H, float eps, int write_resid, int vocab, cudaStream_t stream) {
+  if (!out || H < 1) return Q3_ERR_ARGUMENT;
   if (!ids && !resid) return Q3_ERR_ARGUMENT;
   if ((ids && !table) || (add_ids && !add_table)) return Q3_ERR_ARGUMENT;
   if (write_resid && !resid) return Q3_ERR_ARGUMENT;
   if (post_w && !pending) return Q3_ERR_ARGUMENT;
+  if (pending_parts < 0 || (pending_parts && (!pending || part_stride < 0))) return Q3_ERR_ARGUMENT;
   if (dtype == Q3_DTYPE_F32)
-    return launch_fused_post_norm<float>(pending, post_w, post_eps, resid, ids, table, add_ids, add_table, rows, w, out,
-                                         num_rows, H, eps, write_resid, vocab, stream);
+    return launch_fused_post_norm<float>(pending, pending_parts, part_stride, post_w, post_eps, resid, ids, table, add_ids, add_table, add_vec, rows,
+                                         w, out, num_rows, H, eps, write_resid, vocab, stream);
   if (dtype == Q3_DTYPE_BF16)
-    return launch_fused_post_norm<bf16>(pending, post_w, post_eps, resid, ids, table, add_ids, add_table, rows, w, out,
-                                        num_rows, H, eps, write_resid, vocab, stream);
+    return launch_fused_post_norm<bf16>(pending, pending_parts, part_stride, post_w, post_eps, resid, ids, table, add_ids, add_table, add_vec, rows,
+                                        w, out, num_rows, H, eps, write_resid, vocab, stream);
   return Q3_ERR_ARGUMENT;
 }
 
@@ -414,4 +435,75 @@ Q3_EXPORT int q3_clamped_glu(int dtype, const void* gu, void* out, int num_rows,
   else
     return Q3_ERR_ARGUMENT;
   return q3_launch_status();
+}
+
+// ---- gated slice of a second embedding: out[t, i] = gelu_tanh(gate[t, i]) * table[ids[t], offset + i] ----
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), in fp32.
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const T* __restrict__ gate, const int* __restrict__ ids,
+                                      const T* __restrict__ table, long table_stride, int offset, int vocab,
+                                      T* __restrict__ out, long total, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / n;
+  const int i = (int)(idx - t * n);
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const float z = to_f32(gate[idx]);
+  const float g = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  out[idx] = from_f32<T>(g * to_f32(table[(long)id * table_stride + offset + i]));
+}
+
+// gate, out: dense [num_rows, n]; table: [vocab, table_stride] of which columns offset .. offset + n - 1 are read.
+Q3_EXPORT int q3_gelu_gate_rows(int dtype, const void* gate, const int* ids, const void* table, long table_stride,
+                                int offset, int vocab, void* out, int num_rows, int n, cudaStream_t stream) {
+  if (!gate || !ids || !table || !out || n < 1 || offset < 0 || offset + n > table_stride || vocab < 1)
+    return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * n;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(gelu_gate_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate, ids,
+                   (const float*)table, table_stride, offset, vocab, (float*)out, total, n);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(gelu_gate_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate, ids,
+                   (const bf16*)table, table_stride, offset, vocab, (bf16*)out, total, n);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// ---- squared ReLU over the leading columns of a product: out[t, i] = max(x[t, i], 0)^2, i < n ----
+// x rows are x_stride apart (a product may carry further columns behind the n, e.g. a gate's logit).
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, long x_stride, T* __restrict__ out, long total, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long t = idx / n;
+  const int i = (int)(idx - t * n);
+  const float v = fmaxf(to_f32(x[t * x_stride + i]), 0.f);
+  out[idx] = from_f32<T>(v * v);
+}
+
+Q3_EXPORT int q3_relu_squared(int dtype, const void* x, long x_stride, void* out, int num_rows, int n,
+                              cudaStream_t stream) {
+  if (!x || !out || n < 1 || x_stride < n) return Q3_ERR_ARGUMENT;
+  const long total = (long)num_rows * n;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, x_stride,
+                   (float*)out, total, n);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(relu_squared_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, x_stride, (bf16*)out,
+                   total, n);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }

@@ -1,0 +1,167 @@
+// A short causal convolution over time on every channel of a fused q/k/v projection, followed by
+// what the attention needs of its result: rotation of q and k, and the write of k and v into their
+// cache pages.
+//
+//   y_t[c] = sum_j w[c, j] * u_(t - taps + 1 + j)[c]          (zeros before the sequence's start)
+//
+// u is the projection's output.  The last taps - 1 rows of u of every sequence live in a state slot
+// (fp32 [taps - 1, C], row m holds position start - (taps - 1) + m), so that a step continues where
+// the last one stopped; conv_state_update writes them after conv_rope_store has read the old ones.
+// The convolution accumulates in fp32 in tap order; its result is rotated in fp32 and rounded once.
+//
+// conv_rope_store: one block per token.  The token's C results are kept in shared memory, then
+//   q heads: pairs (i, i + pairs) of a head turn by position * inv_freq[i], written to q_out
+//   k heads: the same, written to the token's row of k_pages
+//   v heads: multiplied by value_scale, written to the token's row of v_pages
+// Keys have D elements a head, values Dv.
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 16
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_rope_store_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int taps,
+                       const float* __restrict__ conv_state, const int* __restrict__ positions,
+                       const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ state_slots, const float* __restrict__ inv_freq, int rot_pairs,
+                       T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                       const int* __restrict__ block_table, int max_pages, int ps, int nq, int nkv, int D, int Dv,
+                       float value_scale, int write_kv) {
+  extern __shared__ float ys[];  // C
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const int p = positions[t];
+  const int Cq = nq * D, Ck = nkv * D, C = Cq + Ck + nkv * Dv;
+  const int n = t - cu_seqlens[b];  // the token's place in its sequence's portion
+  const T* xrow = x + (long)t * x_stride;
+  if (taps > 0) {
+    const float* srow = conv_state + (long)state_slots[b] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;  // how many tokens before this one
+        const float u = n - back >= 0 ? to_f32(xrow[-(long)back * x_stride + c])
+                                      : srow[(long)(taps - 1 + n - back) * C + c];
+        acc = fmaf(w[(long)c * taps + j], u, acc);
+      }
+      ys[c] = acc;
+    }
+  } else {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) ys[c] = to_f32(xrow[c]);
+  }
+  __syncthreads();
+  const int page = write_kv ? block_table[(long)b * max_pages + p / ps] : 0;
+  const int dims = 2 * rot_pairs;
+  // q and k heads: an element of the first half of the rotated part writes both elements of its pair
+  for (int c = threadIdx.x; c < Cq + Ck; c += blockDim.x) {
+    const bool is_q = c < Cq;
+    if (!is_q && !write_kv) continue;
+    const int hc = is_q ? c : c - Cq;
+    const int head = hc / D, e = hc - head * D;
+    T* dst = is_q ? q_out + (long)t * Cq + hc
+                  : k_pages + ((((long)page * nkv + head) * ps + p % ps) * D + e);
+    if (e >= dims) {
+      *dst = from_f32<T>(ys[c]);
+    } else if (e < rot_pairs) {
+      float sn, cs;
+      sincosf((float)p * inv_freq[e], &sn, &cs);
+      const float u = ys[c], v = ys[c + rot_pairs];
+      dst[0] = from_f32<T>(u * cs - v * sn);
+      dst[rot_pairs] = from_f32<T>(v * cs + u * sn);
+    }
+  }
+  if (write_kv)
+    for (int c = threadIdx.x; c < nkv * Dv; c += blockDim.x) {
+      const int head = c / Dv, e = c - head * Dv;
+      v_pages[(((long)page * nkv + head) * ps + p % ps) * Dv + e] = from_f32<T>(ys[Cq + Ck + c] * value_scale);
+    }
+}
+
+// x: [T, C] rows x_stride apart, C = nq * D + nkv * D + nkv * Dv (q heads, k heads, v heads); w: fp32
+// [C, taps] (taps = 0: no convolution, conv_state unused); conv_state: fp32 [slots, taps - 1, C];
+// inv_freq: fp32 [rot_pairs] or rot_pairs = 0; q_out: dense [T, nq * D]; k_pages [pages, nkv, ps, D],
+// v_pages [pages, nkv, ps, Dv].
+Q3_EXPORT int q3_conv_rope_store(int dtype, const void* x, long x_stride, const float* w, int taps,
+                                 const float* conv_state, const int* positions, const int* token_seq,
+                                 const int* cu_seqlens, const int* state_slots, const float* inv_freq, int rot_pairs,
+                                 void* q_out, void* k_pages, void* v_pages, const int* block_table, int max_pages,
+                                 int ps, int num_tokens, int nq, int nkv, int D, int Dv, float value_scale,
+                                 int write_kv, cudaStream_t stream) {
+  if (!x || !positions || !token_seq || !cu_seqlens || !q_out) return Q3_ERR_ARGUMENT;
+  if (taps < 0 || taps > CONV_MAX_TAPS) return Q3_ERR_UNSUPPORTED;
+  if (taps > 0 && (!w || !state_slots || (taps > 1 && !conv_state))) return Q3_ERR_ARGUMENT;
+  if (write_kv && (!k_pages || !v_pages || !block_table || ps < 1)) return Q3_ERR_ARGUMENT;
+  if (nq < 1 || nkv < 1 || D < 1 || Dv < 1 || rot_pairs < 0 || 2 * rot_pairs > D || (rot_pairs && !inv_freq))
+    return Q3_ERR_ARGUMENT;
+  if (num_tokens == 0) return Q3_OK;
+  const size_t smem = (size_t)(nq * D + nkv * D + nkv * Dv) * sizeof(float);
+  if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(conv_rope_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(conv_rope_store_kernel<float>, dim3(num_tokens), dim3(256), smem, stream, (const float*)x, x_stride,
+                   w, taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs,
+                   (float*)q_out, (float*)k_pages, (float*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv,
+                   value_scale, write_kv);
+  } else if (dtype == Q3_DTYPE_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(conv_rope_store_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch_pdl(conv_rope_store_kernel<bf16>, dim3(num_tokens), dim3(256), smem, stream, (const bf16*)x, x_stride, w,
+                   taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs, (bf16*)q_out,
+                   (bf16*)k_pages, (bf16*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv, value_scale, write_kv);
+  } else {
+    return Q3_ERR_ARGUMENT;
+  }
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}
+
+// The last taps - 1 rows of u of every sequence after this step: rows of the step where it brought
+// enough, else older rows of the state moved up.  One thread per (sequence, channel) reads all it
+// needs before it writes.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ x, long x_stride, float* __restrict__ conv_state,
+                                         const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                                         int taps, int C, int num_seqs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)num_seqs * C) return;
+  const int b = (int)(idx / C), c = (int)(idx - (long)b * C);
+  const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+  float* srow = conv_state + (long)state_slots[b] * (taps - 1) * C;
+  float keep[CONV_MAX_TAPS];
+#pragma unroll
+  for (int m = 0; m < CONV_MAX_TAPS - 1; ++m) {
+    if (m >= taps - 1) break;
+    const int li = n - (taps - 1) + m;  // the row's place in this step's portion
+    keep[m] = li >= 0 ? to_f32(x[(long)(t0 + li) * x_stride + c]) : srow[(long)(m + n) * C + c];
+  }
+#pragma unroll
+  for (int m = 0; m < CONV_MAX_TAPS - 1; ++m) {
+    if (m >= taps - 1) break;
+    srow[(long)m * C + c] = keep[m];
+  }
+}
+
+Q3_EXPORT int q3_conv_state_update(int dtype, const void* x, long x_stride, float* conv_state, const int* cu_seqlens,
+                                   const int* state_slots, int taps, int C, int num_seqs, cudaStream_t stream) {
+  if (!x || !conv_state || !cu_seqlens || !state_slots || C < 1) return Q3_ERR_ARGUMENT;
+  if (taps < 2) return Q3_OK;  // nothing is carried
+  if (taps > CONV_MAX_TAPS) return Q3_ERR_UNSUPPORTED;
+  const long total = (long)num_seqs * C;
+  if (total == 0) return Q3_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e;
+  if (dtype == Q3_DTYPE_F32)
+    e = launch_pdl(conv_state_update_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, x_stride,
+                   conv_state, cu_seqlens, state_slots, taps, C, num_seqs);
+  else if (dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(conv_state_update_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, x_stride,
+                   conv_state, cu_seqlens, state_slots, taps, C, num_seqs);
+  else
+    return Q3_ERR_ARGUMENT;
+  return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+}

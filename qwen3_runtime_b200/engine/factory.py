@@ -48,7 +48,10 @@ def load_model(model_dir: str | Path, *, dtype: str = "bfloat16", device="cuda",
     ``pin_path``: a config.json that the folder's model has to match (checked before any weight
     is read)."""
     _arch, config = load_config(model_dir, pin_path)
-    model = build_model(config, SafetensorsDir(model_dir), dtype=dtype, device=device, ops=ops)
+    source = SafetensorsDir(model_dir)
+    if hasattr(config, "with_tensor_shapes"):  # sizes that config.json leaves to the stored tensors
+        config = config.with_tensor_shapes(source.shape)
+    model = build_model(config, source, dtype=dtype, device=device, ops=ops)
     return model, config, read_config_json(model_dir)
 
 

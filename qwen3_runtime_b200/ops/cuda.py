@@ -55,8 +55,11 @@ _SIGNATURES = {
         "q3_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "q3_add_bias": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "q3_logit_scale_cap": [c_void_p, c_long, c_float, c_float, c_void_p],
-        "q3_fused_post_norm": [c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "q3_fused_post_norm": [c_int, c_void_p, c_int, c_long, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "q3_gelu_gate_rows": [c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_int,
+                              c_void_p],
+        "q3_relu_squared": [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
         "q3_clamped_glu": [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p],
     },
     "latent_attention": {
@@ -90,7 +93,12 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p],
         "q3_expert_down": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                            c_void_p, c_void_p],
-        "q3_expert_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "q3_expert_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_int,
+                              c_void_p],
+        "q3_expert_up": [c_int, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                         c_void_p, c_void_p, c_int, c_void_p],
+        "q3_expert_up_tc": [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                            c_void_p, c_void_p, c_int, c_void_p],
     },
     "rope_kv": {
         "q3_qk_norm_rope_store": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
@@ -100,8 +108,21 @@ _SIGNATURES = {
     },
     "attention_generic": {
         "q3_paged_attention_generic": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                       c_void_p],
+                                       c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                       c_int, c_void_p],
+    },
+    "linear_state": {
+        "q3_decayed_state_scan": [c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_long,
+                                  c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "q3_head_norm_gate": [c_int, c_void_p, c_void_p, c_float, c_void_p, c_long, c_void_p, c_long, c_float, c_int,
+                              c_int, c_int, c_void_p],
+    },
+    "short_conv": {
+        "q3_conv_rope_store": [c_int, c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "q3_conv_state_update": [c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "attention_decode": {
         "q3_paged_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -280,18 +301,28 @@ class CudaOps:
 
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
-                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None):
+                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None,
+                   add_vector=None):
         """RMSNorm of ``resid (+ pending)`` or of ``table[ids] (+ pending)``; see csrc/norm.cu.
         ``pending`` is ``[rows, H]`` of the output's type, or fp32 ``[parts, rows, H]``: the
         partial sums of a product (:meth:`linear` with ``partial_sums``), added in order.
         ``post_weight`` / ``post_eps``: what is pending is RMS-normalised with this weight before it
-        is added; ``add_ids`` / ``add_table``: embedding rows added to the sum as well."""
-        H = weight.numel()
+        is added; ``add_ids`` / ``add_table``: embedding rows added to the sum as well;
+        ``add_vector`` (float32 ``[H]``): added to every row's sum.  ``weight=None``: nothing is
+        normalised, ``out`` gets the sum itself, rounded to its type."""
+        H = out.shape[-1]
         n = out.shape[0] if num_rows is None else num_rows
         vocab = table.shape[0] if table is not None else 0
-        if post_weight is not None or add_ids is not None:
-            if pending is not None and (pending.dim() != 2 or pending.dtype != out.dtype
-                                        or not pending.is_contiguous()):
+        if add_vector is not None and (add_vector.dtype != torch.float32 or add_vector.numel() != H
+                                       or not add_vector.is_contiguous()):
+            raise KernelError("fused_norm: add_vector is a dense float32 vector of the rows' width")
+        if post_weight is not None or add_ids is not None or add_vector is not None or weight is None:
+            pparts = pstride = 0
+            if pending is not None and pending.dim() == 3:
+                if pending.dtype != torch.float32 or pending.stride(2) != 1 or pending.stride(1) != H:
+                    raise KernelError("fused_norm: partial sums are fp32 [parts, rows, H] with dense rows")
+                pparts, pstride = pending.shape[0], pending.stride(0)
+            elif pending is not None and (pending.dtype != out.dtype or not pending.is_contiguous()):
                 raise KernelError("fused_norm: a pending output that is normalised first is dense [rows, H] "
                                   "of the output's type")
             if add_table is not None:
@@ -301,9 +332,9 @@ class CudaOps:
                 self._costs(n * H * (2 * e + (4 if resid is not None else 0) + (4 if write_resid else 0)
                                      + (e if add_ids is not None or table is not None else 0)))
             self._call("norm", "q3_fused_post_norm", "fused_post_norm", _dtype_code(out.dtype), _ptr(pending),
-                       _ptr(post_weight), float(post_eps), _ptr(resid), _ptr(ids), _ptr(table), _ptr(add_ids),
-                       _ptr(add_table), _ptr(rows), _ptr(weight), _ptr(out), n, H, float(eps), int(bool(write_resid)),
-                       vocab)
+                       pparts, pstride, _ptr(post_weight), float(post_eps), _ptr(resid), _ptr(ids), _ptr(table), _ptr(add_ids),
+                       _ptr(add_table), _ptr(add_vector), _ptr(rows), _ptr(weight), _ptr(out), n, H, float(eps),
+                       int(bool(write_resid)), vocab)
             return out
         parts = stride = 0
         if pending is not None and pending.dim() == 3:
@@ -358,6 +389,108 @@ class CudaOps:
         self._call("norm", "q3_clamped_glu", "clamped_glu", _dtype_code(out.dtype), _ptr(gate_up), _ptr(out),
                    out.shape[0], F, float(limit), float(alpha), float(up_offset))
         return out
+
+    def relu_squared(self, x, out):
+        """``out[t, i] = max(x[t, i], 0)^2`` for the leading ``out.shape[1]`` columns of ``x`` (rows of ``x``
+        may be wider)."""
+        n = out.shape[-1]
+        if x.stride(1) != 1 or x.shape[1] < n or not out.is_contiguous() or x.dtype != out.dtype:
+            raise KernelError("relu_squared: rows of at least the output's width, dense output of the same type")
+        if self.timing is not None:
+            self._costs(2 * out.shape[0] * n * out.element_size())
+        self._call("norm", "q3_relu_squared", "relu_squared", _dtype_code(out.dtype), _ptr(x), x.stride(0), _ptr(out),
+                   out.shape[0], n)
+        return out
+
+    def gelu_gate_rows(self, gate, ids, table, offset, out):
+        """``out[t, i] = gelu_tanh(gate[t, i]) * table[ids[t], offset + i]`` (csrc/norm.cu)."""
+        T, n = gate.shape
+        if (not gate.is_contiguous() or not out.is_contiguous() or out.shape != gate.shape or table.stride(1) != 1
+                or table.dtype != gate.dtype or offset + n > table.shape[1]):
+            raise KernelError("gelu_gate_rows: dense [rows, n] gate and output, a table of the same type")
+        self._call("norm", "q3_gelu_gate_rows", "gelu_gate_rows", _dtype_code(gate.dtype), _ptr(gate), _ptr(ids),
+                   _ptr(table), table.stride(0), int(offset), table.shape[0], _ptr(out), T, n)
+        return out
+
+    # ---- decayed matrix state (csrc/linear_state.cu) and short convolution (csrc/short_conv.cu) ----
+    def decayed_state_scan(self, q, k, v, *, state, cu_seqlens, state_slots, num_seqs, decay_logits=None,
+                           decay_bias=None, tau=1.0, head_decay=None, inv_freq=None, positions=None, q_scale=1.0,
+                           k_scale=1.0):
+        """``S_t = diag(a_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` per (sequence, head) on the float32
+        state ``[slots, H, D, Dv]`` of the sequences' slots; returns float32 ``o`` ``[T, H, Dv]``.
+        ``q, k`` ``[T, H, D]``, ``v`` ``[T, H, Dv]`` (views of wider rows allowed).  The decay is
+        ``sigmoid(decay_logits + decay_bias)^(1 / tau)`` per key channel, or ``head_decay`` (float32
+        ``[H]``) per head.  ``inv_freq`` (float32 ``[pairs]``): q and k are rotated first (pair i =
+        elements i and i + pairs); then multiplied by ``q_scale`` / ``k_scale``."""
+        T, H, D = q.shape
+        Dv = v.shape[2]
+        for x, what in ((q, "q"), (k, "k"), (v, "v")):
+            if x.stride(2) != 1 or x.stride(1) != x.shape[2]:
+                raise KernelError(f"decayed_state_scan: the heads of {what} lie side by side in a row")
+        z = decay_logits
+        if z is not None and (z.shape != q.shape or z.stride(2) != 1 or z.stride(1) != D):
+            raise KernelError("decayed_state_scan: decay logits are laid out like q")
+        if state.dtype != torch.float32 or state.shape[1:] != (H, D, Dv) or not state.is_contiguous():
+            raise KernelError("decayed_state_scan: the state is dense float32 [slots, H, D, Dv]")
+        out = torch.empty((T, H, Dv), dtype=torch.float32, device=q.device)
+        pairs = inv_freq.numel() if inv_freq is not None else 0
+        if self.timing is not None:
+            e = q.element_size()
+            self._costs(2 * num_seqs * H * D * Dv * 4 + T * H * ((3 if z is not None else 2) * D + Dv) * e
+                        + T * H * Dv * 4, 6.0 * T * H * D * Dv)
+        self._call("linear_state", "q3_decayed_state_scan", "decayed_state_scan", _dtype_code(q.dtype), _ptr(q),
+                   q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
+                   _ptr(decay_bias), 1.0 / float(tau), _ptr(head_decay), _ptr(inv_freq), pairs, _ptr(positions),
+                   float(q_scale), float(k_scale), _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out),
+                   int(num_seqs), H, D, Dv)
+        return out
+
+    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0):
+        """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) * out_scale``:
+        ``o`` float32 ``[T, H, Dv]``, ``gate`` and ``out`` ``[T, H, Dv]`` views of rows, ``weight``
+        float32 ``[Dv]`` or None."""
+        T, H, Dv = o.shape
+        for x in (gate, out):
+            if x.shape != o.shape or x.stride(2) != 1 or x.stride(1) != Dv:
+                raise KernelError("head_norm_gate: gate and output are [T, H, Dv] with the heads side by side")
+        if o.dtype != torch.float32 or not o.is_contiguous():
+            raise KernelError("head_norm_gate: o is dense float32")
+        if self.timing is not None:
+            self._costs(T * H * Dv * (4 + 2 * out.element_size()))
+        self._call("linear_state", "q3_head_norm_gate", "head_norm_gate", _dtype_code(out.dtype), _ptr(o), _ptr(weight),
+                   float(eps), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), float(out_scale), T, H, Dv)
+        return out
+
+    def conv_rope_store(self, x, *, num_heads, num_kv_heads, head_dim, value_dim, conv_weight, conv_state, inv_freq,
+                        positions, token_seq, cu_seqlens, state_slots, num_seqs, block_table, k_pages, v_pages,
+                        page_size, q_out, value_scale=1.0, write_kv=True):
+        """Short causal convolution on every channel of ``x`` ``[T, q heads | k heads | v heads]``
+        (``conv_weight`` float32 ``[C, taps]`` or None; the rows before a step's first token come from
+        ``conv_state`` float32 ``[slots, taps - 1, C]``, which is brought up to date afterwards), rotation
+        of q and k (pair i = elements i and i + pairs, angle ``position * inv_freq[i]``), q into
+        ``q_out``, k and ``value_scale * v`` into the token's page row (csrc/short_conv.cu)."""
+        T = x.shape[0]
+        C = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
+        taps = conv_weight.shape[1] if conv_weight is not None else 0
+        if x.stride(1) != 1 or x.shape[1] != C or not q_out.is_contiguous():
+            raise KernelError("conv_rope_store: rows of q, k and v heads; a dense q output")
+        if taps and (conv_weight.dtype != torch.float32 or not conv_weight.is_contiguous()
+                     or conv_weight.shape[0] != C):
+            raise KernelError("conv_rope_store: a dense float32 weight [channels, taps]")
+        if taps > 1 and (conv_state.dtype != torch.float32 or not conv_state.is_contiguous()
+                         or conv_state.shape[1:] != (taps - 1, C)):
+            raise KernelError("conv_rope_store: the state is dense float32 [slots, taps - 1, channels]")
+        pairs = inv_freq.numel() if inv_freq is not None else 0
+        if self.timing is not None:
+            self._costs(2 * T * C * x.element_size())
+        self._call("short_conv", "q3_conv_rope_store", "conv_rope_store", _dtype_code(x.dtype), _ptr(x), x.stride(0),
+                   _ptr(conv_weight), taps, _ptr(conv_state) if taps > 1 else None, _ptr(positions), _ptr(token_seq),
+                   _ptr(cu_seqlens), _ptr(state_slots), _ptr(inv_freq), pairs, _ptr(q_out), _ptr(k_pages),
+                   _ptr(v_pages), _ptr(block_table), block_table.shape[1] if block_table is not None else 0, page_size,
+                   T, num_heads, num_kv_heads, head_dim, value_dim, float(value_scale), int(bool(write_kv)))
+        if taps > 1:
+            self._call("short_conv", "q3_conv_state_update", "conv_state_update", _dtype_code(x.dtype), _ptr(x),
+                       x.stride(0), _ptr(conv_state), _ptr(cu_seqlens), _ptr(state_slots), taps, C, int(num_seqs))
 
     # ---- attention through a latent (csrc/latent_attention.cu, csrc/head_gemm.cu) ---------------
     def latent_norm_rope_store(self, down, *, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, inv_freq, positions,
@@ -473,11 +606,15 @@ class CudaOps:
         return out
 
     # ---- routed experts (csrc/experts.cu) --------------------------------------------------------
-    def route_top(self, h, router, top, renormalize=False):
+    def route_top(self, h, router, top, renormalize=False, score="sigmoid"):
         """``(chosen int32 [T, top], weights float32 [T, top])``: the float32 router product, the
         ``top`` largest per token in descending order (chosen on the logits, which order the experts as
-        their sigmoids do without the ties of a saturated sigmoid; lowest index on an exact tie), with
-        the sigmoids as weights."""
+        their sigmoids do without the ties of a saturated sigmoid; lowest index on an exact tie).
+        ``score="sigmoid"``: the weights are the chosen logits' sigmoids (``renormalize``: divided by
+        their sum); ``"softmax_chosen"``: the softmax over the chosen logits only."""
+        if score not in ("sigmoid", "softmax_chosen"):
+            raise KernelError(f"route_top: unknown score {score!r}")
+        mode = 2 if score == "softmax_chosen" else int(bool(renormalize))
         T, W = h.shape
         E = router.shape[0]
         if router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != W or h.stride(1) != 1:
@@ -489,24 +626,33 @@ class CudaOps:
             self._costs(E * W * 4 + T * W * h.element_size(), 2.0 * T * E * W)
         self.launches += 1  # two kernels: the logits, then the choice
         self._call("experts", "q3_route_top", "route_top", _dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(router),
-                   T, E, W, top, int(bool(renormalize)), _ptr(logits), _ptr(chosen), _ptr(weights))
+                   T, E, W, top, mode, _ptr(logits), _ptr(chosen), _ptr(weights))
         return chosen, weights
 
-    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit, alpha, up_offset, weight_on="input",
-                       shared=None):
+    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit=0.0, alpha=1.0, up_offset=0.0,
+                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None):
         """Every token through its chosen experts: ``gate_up`` ``[E, 2F, W]`` (gate rows, then up
         rows), ``down`` ``[E, W, F]``; the slots are grouped by expert on the device, each expert's two
         products run over its slots only, and a token's results (and ``shared`` ``[T, W]``) are summed
-        in float32."""
+        in float32.  ``activation="relu2"``: the experts have no gate, ``gate_up`` is the up weight
+        ``[E, F, W]`` and the unit is the squared ReLU (the weight then multiplies the output).
+        ``shared_gate`` ``[T]`` (a view of one column will do): ``shared`` is multiplied by its sigmoid."""
         T, W = h.shape
+        gated = activation == "clamped_glu"
+        if activation not in ("clamped_glu", "relu2"):
+            raise KernelError(f"routed_experts: unknown activation {activation!r}")
         E, F2, _ = gate_up.shape
-        F, top = F2 // 2, chosen.shape[1]
+        F, top = (F2 // 2 if gated else F2), chosen.shape[1]
         S = T * top
         dev = h.device
         if not (gate_up.is_contiguous() and down.is_contiguous() and down.shape == (E, W, F) and h.stride(1) == 1):
-            raise KernelError("routed_experts: dense gate_up [E, 2F, W] and down [E, W, F]")
+            raise KernelError("routed_experts: dense gate_up [E, 2F, W] (or up [E, F, W]) and down [E, W, F]")
         if shared is not None and (shared.shape != (T, W) or not shared.is_contiguous() or shared.dtype != h.dtype):
             raise KernelError("routed_experts: the shared expert's result is dense [tokens, width]")
+        if not gated and weight_on != "output":
+            raise KernelError("routed_experts: experts without a gate take their weight on the output")
+        if shared_gate is not None and (shared is None or shared_gate.shape != (T,) or shared_gate.dtype != h.dtype):
+            raise KernelError("routed_experts: one gate logit per token, of the activations' type")
         plan = torch.empty(2 * (E + 1) + S, dtype=torch.int32, device=dev)
         offsets, tile_offsets, order = plan[: E + 1], plan[E + 1: 2 * (E + 1)], plan[2 * (E + 1):]
         # bfloat16 with 16-byte rows: the products run on the tensor cores, in row tiles of 64 slots when
@@ -522,8 +668,16 @@ class CudaOps:
         code, e = _dtype_code(h.dtype), h.element_size()
         on_input = weight_on == "input"
         if self.timing is not None:  # every chosen expert's weights once, or once per slot when slots are few
-            self._costs(min(S, E) * 2 * F * W * e + T * W * e + S * F * e, 4.0 * S * F * W, f" {S}x{W}->2x{F}")
-        if tensor_cores:
+            n_up = 2 if gated else 1
+            self._costs(min(S, E) * n_up * F * W * e + T * W * e + S * F * e, 2.0 * n_up * S * F * W,
+                        f" {S}x{W}->{n_up}x{F}")
+        if not gated and tensor_cores:
+            self._call("experts", "q3_expert_up_tc", "expert_up_tc", _ptr(h), h.stride(0), _ptr(gate_up), _ptr(mid), S,
+                       E, F, W, top, bm, _ptr(offsets), _ptr(tile_offsets), _ptr(order), 1)
+        elif not gated:
+            self._call("experts", "q3_expert_up", "expert_up", code, _ptr(h), h.stride(0), _ptr(gate_up), _ptr(mid), S,
+                       E, F, W, top, _ptr(offsets), _ptr(tile_offsets), _ptr(order), 1)
+        elif tensor_cores:
             self._call("experts", "q3_expert_gate_up_tc", "expert_gate_up_tc", _ptr(h), h.stride(0), _ptr(gate_up),
                        _ptr(mid), S, E, F, W, top, bm, _ptr(offsets), _ptr(tile_offsets), _ptr(order), _ptr(weights),
                        int(on_input), float(limit), float(alpha), float(up_offset))
@@ -542,7 +696,8 @@ class CudaOps:
         if self.timing is not None:
             self._costs((S + T + (T if shared is not None else 0)) * W * e)
         self._call("experts", "q3_expert_combine", "expert_combine", code, _ptr(y),
-                   None if on_input else _ptr(weights), _ptr(shared), _ptr(out), T, W, top)
+                   None if on_input else _ptr(weights), _ptr(shared), _ptr(shared_gate),
+                   shared_gate.stride(0) if shared_gate is not None else 0, _ptr(out), T, W, top)
         return out
 
     # ---- position encoding + cache write -----------------------------------------------
@@ -581,13 +736,20 @@ class CudaOps:
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
-                        token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None):
-        """Causal attention of every token of the step over its sequence's pages."""
+                        token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
+                        value_dim=None):
+        """Causal attention of every token of the step over its sequence's pages.  ``value_dim``:
+        values have a size of their own (``v_pages`` ``[pages, kv heads, page, value_dim]``); ``out`` may
+        then be a view of wider rows, head h at column ``h * value_dim``."""
         T = out.shape[0]
         if head_dim % 8 or head_dim > 256:
             raise KernelError(
                 f"paged_attention: head_dim={head_dim} is not supported (multiples of 8 up to 256 are)")
-        if (step is not None and step.decode_only and out.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
+        Dv = int(value_dim or head_dim)
+        dense = out.stride(0) == num_heads * Dv and Dv == head_dim
+        if Dv > 256 or out.stride(1) != 1:
+            raise KernelError(f"paged_attention: value_dim={Dv} is not supported (up to 256, unit stride)")
+        if (dense and step is not None and step.decode_only and out.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             return self.paged_attention_decode(
                 q, q_stride, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, k_pages=k_pages,
@@ -595,7 +757,7 @@ class CudaOps:
                 out=out, page_size=page_size, scale=scale, window=window, num_seqs=step.num_seqs,
                 max_kv_len=step.captured_width * page_size or step.max_kv_len, step=step,
                 num_splits=decode_slices, longest=getattr(step, "kv_longest", None))
-        if (step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
+        if (dense and step is not None and out.dtype == torch.bfloat16 and head_dim in (64, 128)
                 and num_heads // num_kv_heads <= 16 and q_stride % 8 == 0):
             # portions of prompts on the tensor-core kernel, one-token sequences on the split-KV kernel
             group = num_heads // num_kv_heads
@@ -646,8 +808,8 @@ class CudaOps:
             self._costs(*self._attention_cost(step, num_heads, num_kv_heads, head_dim, out))
         self._call("attention_generic", "q3_paged_attention_generic", "paged_attention",
                    _dtype_code(out.dtype), _ptr(q), q_stride, _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
-                  block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), T, num_heads, num_kv_heads,
-                  head_dim, page_size, float(scale), int(window or 0))
+                  block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), out.stride(0), T, num_heads,
+                  num_kv_heads, head_dim, Dv, page_size, float(scale), int(window or 0))
         return out
 
     @staticmethod

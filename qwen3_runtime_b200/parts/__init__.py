@@ -1,4 +1,6 @@
-from . import attention, block, experts, feed_forward, latent_attention, norm, position  # noqa: F401  (register the built-in parts)
+# importing the modules registers the built-in parts
+from . import (attention, block, conv_attention, experts, feed_forward, latent_attention, linear_state,  # noqa: F401
+               norm, position, token_side)
 from .base import (
     BuildContext,
     ParamSpec,

@@ -1,6 +1,6 @@
 """What every part is, and the registry that finds a part class by category and kind.
 
-Categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``block``.  A part is
+Categories: ``norm``, ``position``, ``mixer``, ``feed_forward``, ``side_input``, ``block``.  A part is
 built from a :class:`PartSpec` (its sizes and constants) and a :class:`BuildContext`
 (dtype, device, kernel table); it declares its tensors with :meth:`Part.param_specs`
 (names relative to the part's own prefix) and receives them, already on the device,
@@ -17,7 +17,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "block")
 
 
 @dataclass(frozen=True)
@@ -160,6 +160,8 @@ class ResidualStream:
     leaves it here, so that the output norm, the add and the next input norm are one kernel.
     ``add_source``: the embedding rows are to be added to the sum once more (a looped stack that
     is fed its input again); the next norm does it and clears the flag.
+    ``add_vector``: a float32 vector of the model's width that the next norm adds to every row of
+    the sum (and then forgets): a learned offset per pass of a loop.
     """
 
     def __init__(self, num_tokens: int, hidden_size: int, *, ids: torch.Tensor, table: torch.Tensor):
@@ -171,3 +173,4 @@ class ResidualStream:
         self.pending: torch.Tensor | None = None
         self.pending_norm: tuple[torch.Tensor, float] | None = None
         self.add_source = False
+        self.add_vector: torch.Tensor | None = None

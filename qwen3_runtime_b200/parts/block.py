@@ -1,5 +1,7 @@
 """Arrangement of parts in a block.  ``pre_norm``: x += mixer(norm(x)); x += ff(norm(x))
-(qwen3_runtime/models/qwen3.py:159-187, where each add is fused with the next norm).
+(qwen3_runtime/models/qwen3.py:159-187, where each add is fused with the next norm); the
+feed-forward may be absent, and a ``side_input`` part may add something of its own to the stream
+after the sublayers.
 ``sandwich_norm``: a norm before and after each sublayer, x += norm_b(mixer(norm(x))) and
 x += norm_b(ff(norm(x))), the feed-forward being optional."""
 
@@ -14,31 +16,50 @@ class PreNormBlock(Part):
     def __init__(self, spec, ctx: BuildContext):
         super().__init__(spec, ctx)
         self.mixer = build_part("mixer", spec["mixer"], ctx)
-        self.feed_forward = build_part("feed_forward", spec["feed_forward"], ctx)
         self.mixer_norm = build_part("norm", spec["mixer_norm"], ctx)
-        self.feed_forward_norm = build_part("norm", spec["feed_forward_norm"], ctx)
-        self.children = {
-            spec.get("mixer_prefix", "mixer."): self.mixer,
-            spec.get("feed_forward_prefix", "feed_forward."): self.feed_forward,
-            spec.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm,
-            spec.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm,
-        }
-        # the mixer's output meets this block's second norm; where the feed-forward's output
-        # goes only the model knows (exit_to)
+        self.feed_forward = self.feed_forward_norm = self.side = None
+        if spec.get("feed_forward") is not None:
+            self.feed_forward = build_part("feed_forward", spec["feed_forward"], ctx)
+            self.feed_forward_norm = build_part("norm", spec["feed_forward_norm"], ctx)
+        if spec.get("side_input") is not None:
+            self.side = build_part("side_input", spec["side_input"], ctx)
+        # in this order the block's tensors are listed (and a seeded random model draws them)
+        named = [(spec.get("mixer_prefix", "mixer."), self.mixer),
+                 (spec.get("feed_forward_prefix", "feed_forward."), self.feed_forward),
+                 (spec.get("mixer_norm_prefix", "mixer_norm."), self.mixer_norm),
+                 (spec.get("feed_forward_norm_prefix", "feed_forward_norm."), self.feed_forward_norm),
+                 (spec.get("side_input_prefix", "side_input."), self.side)]
+        self.children = {prefix: part for prefix, part in named if part is not None}
+        # full name -> (part, the part's own name for it); prefixes may be prefixes of one another
+        self._owners = {prefix + name: (part, name) for prefix, part in self.children.items()
+                        for name in part.param_specs()}
+        # the mixer's output meets this block's second norm (or, without a feed-forward, whatever
+        # takes the block's output); where the last sublayer's output goes only the model knows
+        # (exit_to).  A side input folds the stream with the entry norm's kernel.
         self.entry_norm = self.mixer_norm
-        self.mixer.partial_sums_ok = self.feed_forward_norm.adds_partial_sums
+        if self.feed_forward is not None:
+            self.mixer.partial_sums_ok = self.feed_forward_norm.adds_partial_sums
+        elif self.side is not None:
+            self.mixer.partial_sums_ok = self.mixer_norm.adds_partial_sums
+        if self.feed_forward is not None and self.side is not None:
+            self.feed_forward.partial_sums_ok = self.mixer_norm.adds_partial_sums
 
     def exit_to(self, norms) -> None:
         """``norms``: every norm that may fold this block's output into the residual sum."""
-        self.feed_forward.partial_sums_ok = all(n.adds_partial_sums for n in norms)
+        if self.side is not None:
+            return  # what leaves the block is the side input's output, a finished product
+        last = self.feed_forward if self.feed_forward is not None else self.mixer
+        last.partial_sums_ok = all(n.adds_partial_sums for n in norms)
 
     def param_specs(self):
-        return {prefix + name: ps for prefix, part in self.children.items()
-                for name, ps in part.param_specs().items()}
+        return {full: part.param_specs()[name] for full, (part, name) in self._owners.items()}
 
     def load(self, tensors):
-        for prefix, part in self.children.items():
-            part.load({name[len(prefix):]: t for name, t in tensors.items() if name.startswith(prefix)})
+        per_part: dict[int, dict] = {}
+        for full, (part, name) in self._owners.items():
+            per_part.setdefault(id(part), {})[name] = tensors[full]
+        for part in self.children.values():
+            part.load(per_part.get(id(part), {}))
 
     def kernel_groups(self):
         return [g for part in self.children.values() for g in part.kernel_groups()]
@@ -56,8 +77,11 @@ class PreNormBlock(Part):
     def forward(self, stream: ResidualStream, step: StepContext, cache) -> None:
         h = self.mixer_norm.add_norm(stream)
         stream.pending = self.mixer.forward(h, step, cache)
-        h = self.feed_forward_norm.add_norm(stream)
-        stream.pending = self.feed_forward.forward(h, step)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.add_norm(stream)
+            stream.pending = self.feed_forward.forward(h, step)
+        if self.side is not None:
+            self.side.forward(stream, step, lambda s: self.mixer_norm.add_norm(s, normalise=False))
 
 
 class SandwichNormBlock(Part):

@@ -11,6 +11,12 @@ the clamped gated layer
     g = min(W_gate x, limit)   u = clamp(W_up x, -limit, limit)   y = g * sigmoid(alpha g) * (u + up_offset)
     expert(x) = W_down y
 
+``activation="relu2"``: an expert has no gate, expert(x) = W_down relu(W_up x)^2.
+``score="softmax_chosen"``: the weights are the softmax over the chosen logits only.
+``shared_gate="sigmoid"``: the shared expert's result is multiplied by sigmoid(w_sg . h), one number
+per token (the stored ``shared.sg`` ``[1, width]`` rides along as one more row of the shared expert's
+first product).
+
 Tokens are grouped by expert on the device (no host round trip, so a step with experts can be
 captured), each expert's products run over its own tokens only, and the results are summed per
 token in float32.
@@ -32,7 +38,10 @@ class RoutedExperts(Part):
         self.num_experts = int(spec["num_experts"])
         self.top = int(spec["top"])
         self.expert_size = int(spec["expert_size"])
-        self.limit = float(spec["limit"])
+        self.activation = spec.get("activation", "clamped_glu")
+        self.gated = self.activation == "clamped_glu"
+        self.limit = float(spec.get("limit") or 0.0)
+        self.shared_gate = spec.get("shared_gate")
         self.alpha = float(spec.get("alpha", 1.702))
         self.up_offset = float(spec.get("up_offset", 1.0))
         self.score = spec.get("score", "sigmoid")
@@ -40,8 +49,16 @@ class RoutedExperts(Part):
         self.weight_on = spec.get("weight_on", "input")
         self.shared_size = int(spec["shared_size"]) if spec.get("shared_size") else 0
         self.shared_limit = float(spec.get("shared_limit") or self.limit)
-        if self.score != "sigmoid":
-            raise ValueError(f"routed_experts scores with a sigmoid, not {self.score!r}")
+        if self.score not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"routed_experts scores with 'sigmoid' or 'softmax_chosen', not {self.score!r}")
+        if self.activation not in ("clamped_glu", "relu2"):
+            raise ValueError(f"routed_experts: unknown activation {self.activation!r}")
+        if self.gated and not self.limit > 0:
+            raise ValueError("routed_experts: the clamped gated unit needs a positive limit")
+        if not self.gated and self.weight_on != "output":
+            raise ValueError("routed_experts: experts without a gate take their weight on the output")
+        if self.shared_gate not in (None, "sigmoid") or (self.shared_gate and (self.gated or not self.shared_size)):
+            raise ValueError("routed_experts: shared_gate is 'sigmoid' on an ungated shared expert, or absent")
         if self.weight_on not in ("input", "output"):
             raise ValueError("weight_on is 'input' or 'output'")
         if not 1 <= self.top <= self.num_experts:
@@ -52,25 +69,39 @@ class RoutedExperts(Part):
         E, F, W = self.num_experts, self.expert_size, self.hidden_size
         specs = {}
         for e in range(E):
-            specs[f"e{e}.gate"] = ParamSpec((F, W))
+            if self.gated:
+                specs[f"e{e}.gate"] = ParamSpec((F, W))
             specs[f"e{e}.up"] = ParamSpec((F, W))
             specs[f"e{e}.down"] = ParamSpec((W, F))
         specs["router"] = ParamSpec((E, W), "matrix_f32")
         if self.shared_size:
-            specs["shared.gate"] = ParamSpec((self.shared_size, W))
+            if self.gated:
+                specs["shared.gate"] = ParamSpec((self.shared_size, W))
             specs["shared.up"] = ParamSpec((self.shared_size, W))
             specs["shared.down"] = ParamSpec((W, self.shared_size))
+            if self.shared_gate:
+                specs["shared.sg"] = ParamSpec((1, W))
         return specs
 
     def load(self, tensors):
         E = self.num_experts
-        # per expert: gate rows, then up rows
-        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
-                                    for e in range(E)]).contiguous()
+        if self.gated:  # per expert: gate rows, then up rows
+            self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                        for e in range(E)]).contiguous()
+        else:
+            self.gate_up = torch.stack([tensors[f"e{e}.up"] for e in range(E)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         self.router = tensors["router"].contiguous()
-        if self.shared_size:
+        if self.shared_size and self.gated:
             self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            self.shared_down = tensors["shared.down"].contiguous()
+        elif self.shared_size:
+            # the up rows, then (with a gate) the gate's row, then zero rows up to a multiple of 8
+            rows = [tensors["shared.up"]] + ([tensors["shared.sg"]] if self.shared_gate else [])
+            pad = -sum(r.shape[0] for r in rows) % 8
+            if pad:
+                rows.append(rows[0].new_zeros((pad, rows[0].shape[1])))
+            self.shared_gate_up = torch.cat(rows, dim=0).contiguous()
             self.shared_down = tensors["shared.down"].contiguous()
 
     def kernel_groups(self):
@@ -83,8 +114,19 @@ class RoutedExperts(Part):
 
     def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
         ops = self.ops
-        chosen, weights = ops.route_top(h, self.router, self.top, renormalize=self.renormalize)
+        chosen, weights = ops.route_top(h, self.router, self.top, renormalize=self.renormalize, score=self.score)
         shared = None
+        if self.shared_size and not self.gated:
+            up = ops.linear(h, self.shared_gate_up)
+            mid = torch.empty((h.shape[0], self.shared_size), dtype=h.dtype, device=h.device)
+            ops.relu_squared(up, mid)
+            shared = ops.linear(mid, self.shared_down)
+            return ops.routed_experts(h, chosen, weights, self.gate_up, self.down, weight_on="output", shared=shared,
+                                      activation="relu2",
+                                      shared_gate=up[:, self.shared_size] if self.shared_gate else None)
+        if not self.gated:
+            return ops.routed_experts(h, chosen, weights, self.gate_up, self.down, weight_on="output",
+                                      activation="relu2")
         if self.shared_size:
             mid = torch.empty((h.shape[0], self.shared_size), dtype=h.dtype, device=h.device)
             ops.clamped_glu(ops.linear(h, self.shared_gate_up), mid, limit=self.shared_limit, alpha=self.alpha,

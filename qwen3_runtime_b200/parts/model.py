@@ -43,6 +43,8 @@ class DecoderModel:
         """Every stored tensor by its checkpoint name, in a fixed order."""
         s = self.spec
         out: dict[str, ParamSpec] = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        for name, shape, kind in s.shared_tables:
+            out[name] = ParamSpec(tuple(shape), kind)
         for i, block in enumerate(self.blocks):
             prefix = s.block_prefix.format(index=i)
             for name, ps in block.param_specs().items():
@@ -68,6 +70,8 @@ class DecoderModel:
         the model's own tensors only one block's stored tensors are alive at any time."""
         s = self.spec
         self.embed = fetch(s.embed_name).contiguous()
+        for name, _shape, _kind in s.shared_tables:  # before the blocks: their parts may read them
+            self.ctx.shared[name] = fetch(name).contiguous()
         for i, block in enumerate(self.blocks):
             prefix = s.block_prefix.format(index=i)
             block.load({name: fetch(prefix + name) for name in block.param_specs()})
@@ -110,6 +114,8 @@ class DecoderModel:
         for run in s.order:
             if run.add_embedding:
                 stream.add_source = True
+            if run.add_row is not None:
+                stream.add_vector = self.ctx.shared[run.add_row[0]][run.add_row[1]]
             self.blocks[run.block].forward(stream, step, storage.view(run.cache, run.writes))
         if step.num_logit_rows == 0:
             return None

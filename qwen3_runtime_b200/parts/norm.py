@@ -1,5 +1,6 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, all in float32, one rounding at the end
-(qwen3_runtime/layers/ops.py:17-20; residual form :28-37)."""
+(qwen3_runtime/layers/ops.py:17-20; residual form :28-37).  ``weight_offset``: the stored weight
+lies around zero and this is added to it when it is loaded (y = ... * (offset + w))."""
 
 from __future__ import annotations
 
@@ -18,6 +19,7 @@ class RMSNorm(Part):
         self.eps = float(spec["eps"])
         # the stored tensor's name after the part's prefix ("" when the prefix is the whole name)
         self.weight_name = str(spec.get("weight_name", "weight"))
+        self.weight_offset = float(spec.get("weight_offset", 0.0))
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
@@ -25,6 +27,8 @@ class RMSNorm(Part):
 
     def load(self, tensors):
         self.weight = tensors[self.weight_name]
+        if self.weight_offset:
+            self.weight = (self.weight.float() + self.weight_offset).contiguous()
 
     def pending_scale(self) -> tuple[torch.Tensor, float]:
         """This norm as something the next norm applies to what is pending (``ResidualStream.pending_norm``)."""
@@ -34,11 +38,12 @@ class RMSNorm(Part):
         return ["norm"]
 
     def add_norm(self, stream: ResidualStream, rows: torch.Tensor | None = None,
-                 num_rows: int | None = None) -> torch.Tensor:
+                 num_rows: int | None = None, normalise: bool = True) -> torch.Tensor:
         """Fold what is pending into the residual sum and return its normalised rows.
 
         With ``rows`` only those rows are normalised and the residual sum is left as
-        it is (the final norm before the output head)."""
+        it is (the final norm before the output head).  ``normalise=False``: the rows of the sum
+        itself, rounded to the activation type (the stream as the input of a product)."""
         n = stream.num_tokens if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=self.ctx.device)
         keep = rows is None
@@ -49,23 +54,27 @@ class RMSNorm(Part):
             if stream.embed is not None:
                 raise ValueError("the embedding cannot be added again before it was read once")
             extra.update(add_ids=stream.source[0], add_table=stream.source[1])
+        if stream.add_vector is not None:
+            extra.update(add_vector=stream.add_vector)
+        weight = self.weight if normalise else None
         if stream.embed is not None:
             ids, table = stream.embed
             if keep:
                 stream.resid = torch.empty((stream.num_tokens, self.size), dtype=torch.float32,
                                            device=self.ctx.device)
-            self.ops.fused_norm(out, self.weight, self.eps, resid=stream.resid if keep else None,
+            self.ops.fused_norm(out, weight, self.eps, resid=stream.resid if keep else None,
                                 pending=stream.pending, ids=ids, table=table, rows=rows, write_resid=keep,
                                 num_rows=n, **extra)
             if keep:
                 stream.embed = None
         else:
-            self.ops.fused_norm(out, self.weight, self.eps, resid=stream.resid, pending=stream.pending,
+            self.ops.fused_norm(out, weight, self.eps, resid=stream.resid, pending=stream.pending,
                                 rows=rows, write_resid=keep, num_rows=n, **extra)
         if keep:
             stream.pending = None
             stream.pending_norm = None
             stream.add_source = False
+            stream.add_vector = None
         return out
 
 

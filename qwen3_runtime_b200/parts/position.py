@@ -40,15 +40,24 @@ class RotaryNeox(Part):
         super().__init__(spec, ctx)
         self.rotary_dim = int(spec["rotary_dim"])
         self.theta = float(spec["theta"])
-        self.max_positions = int(spec["max_positions"])
+        # None: no tables (and no limit); the mixer's kernel works the angles out from the position
+        # and device_inverse_frequencies()
+        self.max_positions = int(spec["max_positions"]) if spec.get("max_positions") else None
         if self.rotary_dim < 2 or self.rotary_dim % 2:
             raise ValueError(f"rotary_dim={self.rotary_dim} must be a positive even number")
 
     def kernel_groups(self):
-        return ["rope_kv"]
+        return ["rope_kv"] if self.max_positions else []
 
     def position_limit(self):
         return self.max_positions
+
+    def device_inverse_frequencies(self) -> torch.Tensor:
+        """float32 ``[rotary_dim / 2]`` on the device, shared by the parts of one model."""
+        key = ("rope_neox_inv", self.rotary_dim, self.theta)
+        if key not in self.ctx.shared:
+            self.ctx.shared[key] = self.inverse_frequencies().to(self.ctx.device)
+        return self.ctx.shared[key]
 
     def inverse_frequencies(self) -> torch.Tensor:
         """inv_j = 1 / theta^(2j / rotary_dim), computed on the host in float32 exactly as
@@ -57,6 +66,8 @@ class RotaryNeox(Part):
         return 1.0 / (self.theta ** exponents)
 
     def rotation_tables(self):
+        if not self.max_positions:
+            raise ValueError("rope_neox without max_positions keeps no tables")
         key = ("rope_neox", self.rotary_dim, self.theta, self.max_positions)
         if key not in self.ctx.shared:
             inv = self.inverse_frequencies().to(self.ctx.device)

@@ -20,7 +20,8 @@ class TorchOps:
 
     # ---- norms ----------------------------------------------------------------------
     def fused_norm(self, out, weight, eps, *, resid=None, pending=None, ids=None, table=None, rows=None,
-                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None):
+                   write_resid=True, num_rows=None, post_weight=None, post_eps=0.0, add_ids=None, add_table=None,
+                   add_vector=None):
         n = out.shape[0] if num_rows is None else num_rows
         src = rows[:n].long() if rows is not None else torch.arange(n, device=out.device)
         if ids is not None:
@@ -39,8 +40,13 @@ class TorchOps:
             v = v + total
         if add_ids is not None:
             v = v + add_table[add_ids.long()[src]].float()
+        if add_vector is not None:
+            v = v + add_vector.float()
         if write_resid:
             resid[src] = v
+        if weight is None:  # the sum itself, rounded
+            out[:n] = v.to(out.dtype)
+            return out
         var = v.pow(2).mean(-1, keepdim=True)
         out[:n] = ((v * torch.rsqrt(var + eps)) * weight.float()).to(out.dtype)
         return out
@@ -50,6 +56,96 @@ class TorchOps:
         g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
         out.copy_(((g / (1 + torch.exp(-g))) * u).to(out.dtype))
         return out
+
+    def relu_squared(self, x, out):
+        out.copy_((torch.relu(x[:, : out.shape[1]].float()) ** 2).to(out.dtype))
+        return out
+
+    def gelu_gate_rows(self, gate, ids, table, offset, out):
+        z = gate.float()
+        g = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        out.copy_((g * table[ids.long(), offset:offset + gate.shape[1]].float()).to(out.dtype))
+        return out
+
+    # ---- decayed matrix state and short convolution ----------------------------------------
+    @staticmethod
+    def _turn_halves(x, pos, inv_freq):
+        """Pairs (i, i + pairs) of the leading 2 * len(inv_freq) elements of the last axis; x [T, H, n] float."""
+        if inv_freq is None:
+            return x
+        pairs = inv_freq.numel()
+        ang = pos.float()[:, None] * inv_freq.float()[None, :]
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        u, v = x[..., :pairs], x[..., pairs:2 * pairs]
+        return torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * pairs:]], dim=-1)
+
+    def decayed_state_scan(self, q, k, v, *, state, cu_seqlens, state_slots, num_seqs, decay_logits=None,
+                           decay_bias=None, tau=1.0, head_decay=None, inv_freq=None, positions=None, q_scale=1.0,
+                           k_scale=1.0):
+        T, H, D = q.shape
+        Dv = v.shape[2]
+        qf, kf = q.float(), k.float()
+        if inv_freq is not None:
+            qf, kf = self._turn_halves(qf, positions.long(), inv_freq), self._turn_halves(kf, positions.long(), inv_freq)
+        qf, kf = qf * q_scale, kf * k_scale
+        if decay_logits is not None:
+            z = decay_logits.float()
+            if decay_bias is not None:
+                z = z + decay_bias.float().reshape(1, H, D)
+            a = torch.exp(torch.nn.functional.logsigmoid(z) / tau)
+        else:
+            a = head_decay.float().reshape(1, H, 1).expand(T, H, D)
+        out = torch.empty((T, H, Dv), dtype=torch.float32, device=q.device)
+        for b in range(num_seqs):
+            slot = int(state_slots[b])
+            S = state[slot].clone()
+            for t in range(int(cu_seqlens[b]), int(cu_seqlens[b + 1])):
+                S = a[t][:, :, None] * S + kf[t][:, :, None] * v[t].float()[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+            state[slot] = S
+        return out
+
+    def head_norm_gate(self, o, gate, out, *, weight, eps, out_scale=1.0):
+        x = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            x = x * weight.float()
+        g = gate.float()
+        out.copy_((x * (g / (1 + torch.exp(-g))) * out_scale).to(out.dtype))
+        return out
+
+    def conv_rope_store(self, x, *, num_heads, num_kv_heads, head_dim, value_dim, conv_weight, conv_state, inv_freq,
+                        positions, token_seq, cu_seqlens, state_slots, num_seqs, block_table, k_pages, v_pages,
+                        page_size, q_out, value_scale=1.0, write_kv=True):
+        T, C = x.shape
+        nq, nkv, D, Dv = num_heads, num_kv_heads, head_dim, value_dim
+        u = x.float()
+        y = u.clone()
+        taps = conv_weight.shape[1] if conv_weight is not None else 0
+        if taps:
+            for b in range(num_seqs):
+                t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+                slot = int(state_slots[b])
+                old = conv_state[slot].float() if taps > 1 else u.new_zeros((0, C))
+                rows = torch.cat([old, u[t0:t1]])  # row m + n is the portion's token n
+                for n in range(t1 - t0):
+                    acc = u.new_zeros(C)
+                    for j in range(taps):
+                        acc = acc + conv_weight[:, j].float() * rows[n + j]
+                    y[t0 + n] = acc
+                if taps > 1:
+                    conv_state[slot] = rows[rows.shape[0] - (taps - 1):]
+        pos = positions.long()
+        q = self._turn_halves(y[:, : nq * D].reshape(T, nq, D), pos, inv_freq)
+        q_out.copy_(q.reshape(T, nq * D).to(q_out.dtype))
+        if not write_kv:
+            return
+        k = self._turn_halves(y[:, nq * D:(nq + nkv) * D].reshape(T, nkv, D), pos, inv_freq).to(k_pages.dtype)
+        v = (y[:, (nq + nkv) * D:].reshape(T, nkv, Dv) * value_scale).to(v_pages.dtype)
+        for t in range(T):
+            p = int(pos[t])
+            page = int(block_table[int(token_seq[t]), p // page_size])
+            k_pages[page, :, p % page_size, :] = k[t]
+            v_pages[page, :, p % page_size, :] = v[t]
 
     # ---- position encoding + cache write -----------------------------------------------
     def rope_table(self, inv_freq, max_positions):
@@ -94,7 +190,8 @@ class TorchOps:
 
     # ---- attention --------------------------------------------------------------------
     def paged_attention(self, q, q_stride, *, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table,
-                        token_seq, positions, out, page_size, scale, window, step=None):
+                        token_seq, positions, out, page_size, scale, window, step=None, decode_slices=None,
+                        value_dim=None):
         T = out.shape[0]
         D = head_dim
         group = num_heads // num_kv_heads
@@ -173,8 +270,10 @@ class TorchOps:
         return out
 
     # ---- routed experts ----------------------------------------------------------------
-    def route_top(self, h, router, top, renormalize=False):
+    def route_top(self, h, router, top, renormalize=False, score="sigmoid"):
         best = torch.topk(h.float() @ router.float().t(), top, dim=-1)  # on the logits: no saturated ties
+        if score == "softmax_chosen":
+            return best.indices.to(torch.int32), torch.softmax(best.values, dim=-1).float()
         w = torch.sigmoid(best.values)
         if renormalize:
             w = w / w.sum(-1, keepdim=True)
@@ -187,20 +286,26 @@ class TorchOps:
         out.copy_((g * torch.sigmoid(alpha * g) * (u + up_offset)).to(out.dtype))
         return out
 
-    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit, alpha, up_offset, weight_on="input",
-                       shared=None):
+    def routed_experts(self, h, chosen, weights, gate_up, down, *, limit=0.0, alpha=1.0, up_offset=0.0,
+                       weight_on="input", shared=None, activation="clamped_glu", shared_gate=None):
         T, W = h.shape
-        F = gate_up.shape[1] // 2
+        gated = activation == "clamped_glu"
+        F = gate_up.shape[1] // 2 if gated else gate_up.shape[1]
         total = torch.zeros((T, W), dtype=torch.float32, device=h.device)
         for t in range(T):
             for e, w in zip(chosen[t].tolist(), weights[t].tolist()):
                 x = (h[t].float() * w).to(h.dtype) if weight_on == "input" else h[t]
                 gu = (gate_up[e].float() @ x.float()).to(h.dtype)
                 mid = torch.empty((1, F), dtype=h.dtype, device=h.device)
-                self.clamped_glu(gu[None], mid, limit=limit, alpha=alpha, up_offset=up_offset)
+                if gated:
+                    self.clamped_glu(gu[None], mid, limit=limit, alpha=alpha, up_offset=up_offset)
+                else:
+                    self.relu_squared(gu[None], mid)
                 y = (down[e].float() @ mid[0].float()).to(h.dtype).float()
                 total[t] += y if weight_on == "input" else y * w
-        if shared is not None:
+        if shared is not None and shared_gate is not None:
+            total += shared.float() * torch.sigmoid(shared_gate.float())[:, None]
+        elif shared is not None:
             total += shared.float()
         return total.to(h.dtype)
 
