@@ -1,6 +1,6 @@
 // Causal attention over the paged cache for any mix of prompt portions and single
-// decoded tokens: the general kernel (any head_dim that is a multiple of 8 up to
-// 256, a value size of its own up to 256, any head counts, any page size, optional
+// decoded tokens: the general kernel (any head_dim up to 256 (multiples of 8 with
+// 16-byte loads), a value size of its own up to 256, any head counts, any page size, optional
 // window), used by the fp32 path and wherever a specialised kernel refuses a size.
 //
 // One warp per (token, query head).  The query at absolute position p attends to
@@ -49,11 +49,15 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
       row = ((long)page * nkv + kvh) * ps + (j % ps);
       const T* kr = kpages + row * D;
       float dot = 0.f;
-      for (int d = 0; d < D; d += 8) {
-        float kv[8];
-        load8(kr + d, kv);
+      if ((D & 7) == 0) {
+        for (int d = 0; d < D; d += 8) {
+          float kv[8];
+          load8(kr + d, kv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+          for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+        }
+      } else {  // rows that are not 16-byte multiples: one element at a time
+        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
       }
       s = dot * scale;
     }
@@ -97,7 +101,7 @@ Q3_EXPORT int q3_paged_attention_generic(int dtype, const void* q, int q_stride,
                                          int window, cudaStream_t stream) {
   if (!q || !kpages || !vpages || !block_table || !token_seq || !positions || !out) return Q3_ERR_ARGUMENT;
   if (nq < 1 || nkv < 1 || nq % nkv || ps < 1) return Q3_ERR_ARGUMENT;
-  if (D < 8 || D % 8 || D > 256 || Dv < 1 || Dv > 256 || out_stride < (long)nq * Dv) return Q3_ERR_UNSUPPORTED;
+  if (D < 1 || D > 256 || Dv < 1 || Dv > 256 || out_stride < (long)nq * Dv) return Q3_ERR_UNSUPPORTED;
   if (num_tokens == 0) return Q3_OK;
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * D * sizeof(float);

@@ -1,6 +1,6 @@
 """Puladra expressed as data for the generic decoder.
 
-Pre-norm blocks whose norm weights are stored around zero (``1 + w``).  The mixer of a layer is
+Pre-norm blocks whose norms multiply by ``1 + w``, w being the stored tensor.  The mixer of a layer is
 gated linear attention (``gla``) or two mixers side by side on the same input (``parallel``:
 windowed softmax attention with a short convolution on q, k and v, and retention), the
 feed-forward routed squared-ReLU experts with a gated shared one, or absent.  After its sublayers a

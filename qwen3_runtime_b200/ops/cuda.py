@@ -742,9 +742,8 @@ class CudaOps:
         values have a size of their own (``v_pages`` ``[pages, kv heads, page, value_dim]``); ``out`` may
         then be a view of wider rows, head h at column ``h * value_dim``."""
         T = out.shape[0]
-        if head_dim % 8 or head_dim > 256:
-            raise KernelError(
-                f"paged_attention: head_dim={head_dim} is not supported (multiples of 8 up to 256 are)")
+        if head_dim > 256:
+            raise KernelError(f"paged_attention: head_dim={head_dim} is not supported (sizes up to 256 are)")
         Dv = int(value_dim or head_dim)
         dense = out.stride(0) == num_heads * Dv and Dv == head_dim
         if Dv > 256 or out.stride(1) != 1:

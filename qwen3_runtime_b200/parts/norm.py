@@ -1,6 +1,6 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, all in float32, one rounding at the end
 (qwen3_runtime/layers/ops.py:17-20; residual form :28-37).  ``weight_offset``: the stored weight
-lies around zero and this is added to it when it is loaded (y = ... * (offset + w))."""
+is the deviation from this value, which is added to it when it is loaded (y = ... * (offset + w))."""
 
 from __future__ import annotations
 

@@ -26,7 +26,7 @@ def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def offset_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """The model's norm: the stored weight lies around zero and one is added to it."""
+    """The model's norm multiplies by one plus the stored tensor."""
     return unit_rms(x, eps) * (1.0 + w.float())
 
 
