@@ -43,6 +43,9 @@ kinds and a roofline fraction per kind):
                    Qwen3 dense model of equal width, heads and active feed-forward width: one
                    2,048-token prefill and decode steps at batch 8 behind 1,024-token contexts, both
                    device-timed through the step function, with the per-kernel table of each;
+* ``puladra``      the same comparison for the Puladra design (gated linear attention, windowed
+                   attention with a short convolution beside retention, routed squared-ReLU experts,
+                   a per-layer token input) at two layer sizes;
 * ``decode``, ``latency``, ``batch8``, ``throughput``, ``prefill``, ``longctx``: the six closed
                    batches of the reference's own harness (bench/workloads.py:34-43) at Qwen3-4B
                    sizes, with its token budget rule (bench/workloads.py:52-64).
@@ -93,7 +96,23 @@ BASELINE_TOK_S = 693.26
 # (concurrency = requests, prompt tokens, output tokens) of the reference's closed batches
 CLOSED_CASES = {"decode": (1, 256, 512), "latency": (1, 512, 128), "batch8": (8, 256, 128),
                 "throughput": (16, 256, 128), "prefill": (1, 2048, 16), "longctx": (1, 8192, 64)}
-WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", *CLOSED_CASES)
+WORKLOADS = ("default", "decode512", "batch48", "32b", "logesun", "puladra", *CLOSED_CASES)
+
+# Layer sizes for the Puladra design that resemble real models of its kinds of layer: gated linear
+# attention with keys of half and values of the full width, windowed attention with grouped key/value
+# heads and a convolution of four taps beside retention, 64 or 32 routed squared-ReLU experts with a
+# shared one, a per-layer token input of 256.  Four layers each (gla, parallel, gla, parallel), no
+# loop; beside each a Qwen3 dense model of equal width, heads, layers and active feed-forward width.
+PULADRA_SIZES = {
+    "w2048": dict(width=2048, heads=16, gla=dict(heads=16, dim=64, vdim=128, rank=16),
+                  left=dict(heads=16, kv_heads=4, dim=128, vdim=128, conv=4, window=1024),
+                  right=dict(heads=8, dim=64, vdim=128), experts=64, top=6, expert_ff=1408, shared_ff=2816,
+                  side=256, layers=4, vocab=32000),
+    "w4096": dict(width=4096, heads=32, gla=dict(heads=32, dim=64, vdim=128, rank=16),
+                  left=dict(heads=32, kv_heads=8, dim=128, vdim=128, conv=4, window=2048),
+                  right=dict(heads=16, dim=64, vdim=128), experts=32, top=4, expert_ff=2048, shared_ff=2048,
+                  side=256, layers=4, vocab=32000),
+}
 
 # Layer sizes for the Logesun design (attention through a latent with a window and a sink, routed
 # clamped experts with a shared one, norms around every sublayer) that resemble real models of that
@@ -596,8 +615,46 @@ def _dense_twin_config(z: dict):
                        max_position_embeddings=8192, tie_word_embeddings=False)
 
 
+def _puladra_config(z: dict):
+    from qwen3_runtime_b200.config import PuladraConfig
+    from qwen3_runtime_b200.config.puladra_config import (GlaConfig, MoeConfig, ParallelConfig, PuladraLayerConfig,
+                                                          RetentionConfig, RotationConfig, WindowAttentionConfig)
+
+    g, l, r = z["gla"], z["left"], z["right"]
+    gla = GlaConfig(heads=g["heads"], dim=g["dim"], vdim=g["vdim"], tau=16.0, decay_rank=g["rank"])
+    par = ParallelConfig(
+        left=WindowAttentionConfig(heads=l["heads"], kv_heads=l["kv_heads"], dim=l["dim"], vdim=l["vdim"],
+                                   scale=l["dim"] ** -0.5, conv=l["conv"], rot=RotationConfig(l["dim"], 10000.0),
+                                   window=l["window"]),
+        right=RetentionConfig(heads=r["heads"], dim=r["dim"], vdim=r["vdim"],
+                              decay=tuple(1.0 - 2.0 ** (-5 - (i % 8)) for i in range(r["heads"])),
+                              rot=RotationConfig(r["dim"], 10000.0)),
+        left_scale=1.0, right_scale=1.0)
+    moe = MoeConfig(experts=z["experts"], top=z["top"], ff=z["expert_ff"], shared_ff=z["shared_ff"])
+    layers = tuple(PuladraLayerConfig("gla", gla, moe) if i % 2 == 0 else PuladraLayerConfig("parallel", par, moe)
+                   for i in range(z["layers"]))
+    return PuladraConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, layers=layers, logit_scale=1.0,
+                         side_dim=z["side"])
+
+
 def run_logesun(args, pk) -> dict:
-    """Prefill and decode of the Logesun design beside a Qwen3 dense model of equal size."""
+    return run_design_beside_dense(args, pk, "logesun", "Logesun", LOGESUN_SIZES, _logesun_config)
+
+
+def run_puladra(args, pk) -> dict:
+    return run_design_beside_dense(args, pk, "puladra", "Puladra", PULADRA_SIZES, _puladra_config)
+
+
+def _fill_cache(storage) -> None:
+    """Random keys, values, rows and states, so that a decode step behind a pretended context reads
+    finite numbers."""
+    for t in storage.tensors:
+        for x in (t if isinstance(t, tuple) else (t,)):
+            x.normal_(0.0, 0.5)
+
+
+def run_design_beside_dense(args, pk, workload: str, design: str, sizes: dict, make_config) -> dict:
+    """Prefill and decode of a design beside a Qwen3 dense model of equal size."""
     import torch
 
     from qwen3_runtime_b200.engine.factory import build_model, build_runtime
@@ -610,16 +667,15 @@ def run_logesun(args, pk) -> dict:
     rand_ids = make_rand_ids(torch)
     clocks = ClockSampler().start()
     results = {}
-    for size, z in LOGESUN_SIZES.items():
-        for arm, cfg in (("logesun", _logesun_config(z)), ("qwen3_dense", _dense_twin_config(z))):
+    for size, z in sizes.items():
+        for arm, cfg in ((workload, make_config(z)), ("qwen3_dense", _dense_twin_config(z))):
             ops = CudaOps()
             model = build_model(cfg, RandomDeviceSource(expected_tensors_for(cfg), SEED, "cuda"), dtype="bfloat16",
                                 ops=ops)
             tokens = batch * (context + K + W + 64) + PREFILL_TOKENS + 64
             rt = build_runtime(model, block_size=PAGE, num_kv_blocks=-(-tokens // PAGE) + 64, max_num_seqs=batch + 2,
                                cuda_graph=True)
-            for t in rt.storage.tensors:
-                t.normal_(0.0, 0.5)
+            _fill_cache(rt.storage)
             ms_steps, launches = decode_point(rt, ops, torch, rand_ids, batch, context, K, W, sampler=clocks)
             prefill_ms = prefill_point(rt, torch, rand_ids, PREFILL_TOKENS)
             rt.runner.graphs = None
@@ -631,16 +687,16 @@ def run_logesun(args, pk) -> dict:
                 launches_per_decode_step=launches, kernels=kernels)
             del rt, model, ops
             torch.cuda.empty_cache()
-    first = results["w2048/logesun"]
+    first = results[f"w2048/{workload}"]
     return {
-        "metric": "decode tok/s @ batch 8, ctx 1024 (Logesun w2048 sizes, 4 layers, bf16); beside it a Qwen3 dense "
+        "metric": f"decode tok/s @ batch 8, ctx 1024 ({design} w2048 sizes, 4 layers, bf16); beside it a Qwen3 dense "
                   "model of equal size, and one 2048-token prefill of each",
         "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "impl": "ours", "workload": "logesun",
+        "dtype": "bf16", "impl": "ours", "workload": workload,
         "data": "synthetic: seeded random weights N(0,0.02), random token ids; cache pages hold random rows",
-        "config": dict(model="Logesun sizes " + ", ".join(LOGESUN_SIZES), global_batch=batch, seq_len=context,
-                       parallelism="single GPU", sizes=LOGESUN_SIZES,
+        "config": dict(model=f"{design} sizes " + ", ".join(sizes), global_batch=batch, seq_len=context,
+                       parallelism="single GPU", sizes=sizes,
                        l2="weights and cache rows of a step exceed L2; no flush"),
         "results": results, "peaks": pk, "clocks": clocks.summary(),
     }
@@ -655,6 +711,8 @@ def run_workload_ours(args) -> dict:
         return run_32b_ours(args, pk)
     if args.workload == "logesun":
         return run_logesun(args, pk)
+    if args.workload == "puladra":
+        return run_puladra(args, pk)
     cases = workload_prompts(args.workload, np)
     results, cfg, build_s, engine = {}, None, 0.0, None
     clocks = ClockSampler()
@@ -912,8 +970,8 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
     if args.workload == "default":
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
-    elif args.workload == "logesun" and args.impl == "reference":
-        result = {"impl": "reference", "workload": "logesun",
+    elif args.workload in ("logesun", "puladra") and args.impl == "reference":
+        result = {"impl": "reference", "workload": args.workload,
                   "unavailable": "the reference has no model of this design (it serves Qwen3 dense only)"}
     else:
         result = run_workload_reference(args) if args.impl == "reference" else run_workload_ours(args)

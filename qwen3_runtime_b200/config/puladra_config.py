@@ -65,7 +65,8 @@ class GlaConfig:
     @classmethod
     def from_raw(cls, where: str, raw: Mapping[str, Any]) -> "GlaConfig":
         cfg = cls(heads=_positive_int(where, raw, "heads"), dim=_positive_int(where, raw, "dim"),
-                  vdim=_positive_int(where, raw, "vdim"), tau=float(_require(raw, "tau")))
+                  vdim=_positive_int(where, raw, "vdim"), tau=float(_require(raw, "tau")),
+                  decay_rank=int(raw.get("decay_rank") or 0))  # an optional key: a model that is yet to be written
         if not cfg.tau > 0:
             raise ConfigError(f"{where}: tau must be positive")
         return cfg

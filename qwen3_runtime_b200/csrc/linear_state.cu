@@ -8,22 +8,28 @@
 // k_scale; decays, angles, the state and the products with it are fp32, q, k, v and z arrive in the
 // activation type.
 //
-// decayed_state_scan: one block per (32 value columns, head, sequence).  Lane = value column, warp =
-// group of R key rows, so a thread keeps R elements of the state in registers from the sequence's
-// first token of the step to its last.  Tokens are staged CT at a time in shared memory (q, k and
-// decay rows as fp32, already rotated and scaled), every thread runs the CT updates on its rows, the
-// warps' partial outputs are added in warp order.  A token's arithmetic does not depend on where
-// the step's portion starts or ends, so the result has the same bits however a prompt is cut.
+// decayed_state_scan: one block per (32 value columns, head, sequence).  A thread owns eight key
+// rows of one value column of the state and keeps them in registers from the sequence's first token
+// of the step to its last; the row groups of a column are neighbouring lanes of one warp, so a
+// token's output is a shuffle sum over them (a fixed tree) and warps never wait for one another
+// inside a chunk.  Tokens come 16 at a time: while the threads run the updates of one chunk from
+// shared memory (q, k and decay rows as fp32, already rotated and scaled), the next chunk's raw
+// values are already on their way into registers; they are turned into fp32 rows in the other half
+// of the double buffer afterwards.  A token's arithmetic does not depend on where the step's portion
+// starts or ends, so the result has the same bits however a prompt is cut.
 //
 // head_norm_gate: y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :]) * out_scale, one warp
 // per (token, head); w may be absent.
 #include "common.cuh"
 
-#define SCAN_CT 8   // tokens staged at a time
-#define SCAN_R 8    // key rows per thread
+#define SCAN_CT 16  // tokens per chunk
 
-template <typename T>
-__global__ void __launch_bounds__(1024)
+// SCAN_R key rows per thread, SCAN_VT value columns per block; RGP2: row groups per value column (a
+// power of two, 4..32): the block holds RGP2 * SCAN_R >= D key rows.  Four rows a thread and 16
+// columns a block (key sizes up to 128) make four times as many warps as eight and 32 do: a single
+// prompt's scan is a chain of dependent steps whose latencies only other warps can fill.
+template <typename T, int RGP2, int SCAN_R, int SCAN_VT>
+__global__ void __launch_bounds__(SCAN_VT * RGP2)
 decayed_state_scan_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ k, long k_stride,
                           const T* __restrict__ v, long v_stride, const T* __restrict__ z, long z_stride,
                           const float* __restrict__ z_bias, float inv_tau, const float* __restrict__ head_decay,
@@ -31,74 +37,115 @@ decayed_state_scan_kernel(const T* __restrict__ q, long q_stride, const T* __res
                           float q_scale, float k_scale, float* __restrict__ state,
                           const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
                           float* __restrict__ out, int H, int D, int Dv) {
+  constexpr int THREADS = SCAN_VT * RGP2, DP = RGP2 * SCAN_R, CPW = 32 / RGP2;  // columns per warp
+  constexpr int EPT = SCAN_CT * DP / THREADS;                              // row elements per thread and chunk: 4
+  constexpr int VPT = (SCAN_CT * SCAN_VT + THREADS - 1) / THREADS;         // value elements per thread and chunk
   extern __shared__ __align__(16) float scan_smem[];
-  const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int Dp = nwarp * SCAN_R;                 // D rounded up to the rows the block holds
-  float* qs = scan_smem;                          // [CT][Dp]
-  float* ks = qs + SCAN_CT * Dp;                  // [CT][Dp]
-  float* as = ks + SCAN_CT * Dp;                  // [CT][Dp]
-  float* vs = as + SCAN_CT * Dp;                  // [CT][32]
-  float* part = vs + SCAN_CT * 32;                // [nwarp][CT][32]
+  typedef float (*Rows)[SCAN_CT][DP];
+  typedef float (*Vals)[SCAN_CT][SCAN_VT];
+  Rows qs = reinterpret_cast<Rows>(scan_smem);                    // [2][CT][DP]
+  Rows ks = reinterpret_cast<Rows>(scan_smem + 2 * SCAN_CT * DP);
+  Rows as = reinterpret_cast<Rows>(scan_smem + 4 * SCAN_CT * DP);
+  Vals vs = reinterpret_cast<Vals>(scan_smem + 6 * SCAN_CT * DP);  // [2][CT][VT]
+  float (*os)[SCAN_VT] = reinterpret_cast<float (*)[SCAN_VT]>(scan_smem + 6 * SCAN_CT * DP + 2 * SCAN_CT * SCAN_VT);
   pdl_wait();
   pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = lane % RGP2, col = warp * CPW + lane / RGP2;
   const int h = blockIdx.y, b = blockIdx.z;
-  const int j = blockIdx.x * 32 + lane;
+  const int j = blockIdx.x * SCAN_VT + col;
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   const long slot = state_slots[b];
   float* Sg = state + ((slot * H + h) * (long)D) * Dv;
   float S[SCAN_R];
 #pragma unroll
   for (int r = 0; r < SCAN_R; ++r) {
-    const int i = warp * SCAN_R + r;
+    const int i = rg * SCAN_R + r;
     S[r] = (i < D && j < Dv) ? Sg[(long)i * Dv + j] : 0.f;
   }
   const float decay_h = head_decay ? head_decay[h] : 1.f;
-  for (int c0 = t0; c0 < t1; c0 += SCAN_CT) {
-    const int n = min(SCAN_CT, t1 - c0);
-    // stage the chunk: rows beyond D are zero (their state stays zero and adds nothing)
-    for (int x = threadIdx.x; x < n * Dp; x += blockDim.x) {
-      const int c = x / Dp, i = x - c * Dp;
+
+  // what a thread fetches of a chunk: EPT elements of the q, k (and logit) rows, their rotation
+  // partners, VPT values
+  T qr[EPT], kr[EPT], zr[EPT], qo[EPT], ko[EPT], vr[VPT];
+  auto fetch = [&](int c0) {
+#pragma unroll
+    for (int m = 0; m < EPT; ++m) {
+      const int x = tid + m * THREADS, c = x / DP, i = x - c * DP;
+      const long t = c0 + c;
+      const bool live = t < t1 && i < D;
+      qr[m] = live ? q[t * q_stride + h * D + i] : from_f32<T>(0.f);
+      kr[m] = live ? k[t * k_stride + h * D + i] : from_f32<T>(0.f);
+      zr[m] = (live && z) ? z[t * z_stride + h * D + i] : from_f32<T>(0.f);
+      if (live && i < 2 * rot_pairs) {
+        const int other = i < rot_pairs ? i + rot_pairs : i - rot_pairs;
+        qo[m] = q[t * q_stride + h * D + other];
+        ko[m] = k[t * k_stride + h * D + other];
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < VPT; ++m) {
+      const int x = tid + m * THREADS, c = x / SCAN_VT, jj = blockIdx.x * SCAN_VT + (x % SCAN_VT);
+      const long t = c0 + c;
+      vr[m] = (x < SCAN_CT * SCAN_VT && t < t1 && jj < Dv) ? v[t * v_stride + h * Dv + jj] : from_f32<T>(0.f);
+    }
+  };
+  // turn what was fetched into the fp32 rows of buffer `buf`: rows beyond D and tokens beyond the
+  // portion are zero (their state stays zero and adds nothing)
+  auto stage = [&](int c0, int buf) {
+#pragma unroll
+    for (int m = 0; m < EPT; ++m) {
+      const int x = tid + m * THREADS, c = x / DP, i = x - c * DP;
       const long t = c0 + c;
       float qv = 0.f, kv = 0.f, av = 0.f;
-      if (i < D) {
-        qv = to_f32(q[t * q_stride + h * D + i]);
-        kv = to_f32(k[t * k_stride + h * D + i]);
+      if (t < t1 && i < D) {
+        qv = to_f32(qr[m]);
+        kv = to_f32(kr[m]);
         if (i < 2 * rot_pairs) {
           const int pair = i < rot_pairs ? i : i - rot_pairs;
-          const int other = i < rot_pairs ? i + rot_pairs : i - rot_pairs;
           float sn, cs;
           sincosf((float)positions[t] * inv_freq[pair], &sn, &cs);
-          const float qo = to_f32(q[t * q_stride + h * D + other]);
-          const float ko = to_f32(k[t * k_stride + h * D + other]);
+          const float qp = to_f32(qo[m]), kp = to_f32(ko[m]);
           // first of a pair: u cos - v sin; second: v cos + u sin
-          qv = i < rot_pairs ? qv * cs - qo * sn : qv * cs + qo * sn;
-          kv = i < rot_pairs ? kv * cs - ko * sn : kv * cs + ko * sn;
+          qv = i < rot_pairs ? qv * cs - qp * sn : qv * cs + qp * sn;
+          kv = i < rot_pairs ? kv * cs - kp * sn : kv * cs + kp * sn;
         }
         qv *= q_scale;
         kv *= k_scale;
         if (z) {
-          const float zz = to_f32(z[t * z_stride + h * D + i]) + (z_bias ? z_bias[h * D + i] : 0.f);
+          const float zz = to_f32(zr[m]) + (z_bias ? z_bias[h * D + i] : 0.f);
           const float log_sig = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
           av = expf(log_sig * inv_tau);
         } else {
           av = decay_h;
         }
       }
-      qs[x] = qv;
-      ks[x] = kv;
-      as[x] = av;
+      qs[buf][c][i] = qv;
+      ks[buf][c][i] = kv;
+      as[buf][c][i] = av;
     }
-    for (int x = threadIdx.x; x < n * 32; x += blockDim.x) {
-      const int c = x >> 5, jj = blockIdx.x * 32 + (x & 31);
-      vs[x] = jj < Dv ? to_f32(v[(long)(c0 + c) * v_stride + h * Dv + jj]) : 0.f;
+#pragma unroll
+    for (int m = 0; m < VPT; ++m) {
+      const int x = tid + m * THREADS;
+      if (x < SCAN_CT * SCAN_VT) vs[buf][x / SCAN_VT][x % SCAN_VT] = to_f32(vr[m]);
     }
-    __syncthreads();
-    const int i0 = warp * SCAN_R;
-    for (int c = 0; c < n; ++c) {
-      const float vj = vs[c * 32 + lane];
-      const float4* a4 = reinterpret_cast<const float4*>(as + c * Dp + i0);
-      const float4* k4 = reinterpret_cast<const float4*>(ks + c * Dp + i0);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + c * Dp + i0);
+  };
+
+  fetch(t0);
+  stage(t0, 0);
+  __syncthreads();
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += SCAN_CT, buf ^= 1) {
+    const int n = min(SCAN_CT, t1 - c0);
+    const bool more = c0 + SCAN_CT < t1;
+    if (more) fetch(c0 + SCAN_CT);  // in flight while this chunk is computed
+    const int i0 = rg * SCAN_R;
+    // one token's update of this thread's rows; returns its share of the token's output
+    auto update = [&](int c) -> float {
+      const float vj = vs[buf][c][col];
+      const float4* a4 = reinterpret_cast<const float4*>(&as[buf][c][i0]);
+      const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][c][i0]);
+      const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][c][i0]);
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int g = 0; g < SCAN_R / 4; ++g) {
@@ -112,22 +159,57 @@ decayed_state_scan_kernel(const T* __restrict__ q, long q_stride, const T* __res
         acc0 = fmaf(S[4 * g + 2], qq.z, acc0);
         acc1 = fmaf(S[4 * g + 3], qq.w, acc1);
       }
-      part[(warp * SCAN_CT + c) * 32 + lane] = acc0 + acc1;
+      return acc0 + acc1;
+    };
+    int c = 0;
+    for (; c + 4 <= n; c += 4) {  // four tokens' sums over the row groups side by side: their shuffles overlap
+      float acc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = update(c + u);
+#pragma unroll
+      for (int o = 1; o < RGP2; o <<= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+      }
+      if (rg == 0) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) os[c + u][col] = acc[u];
+      }
     }
-    __syncthreads();
-    for (int x = threadIdx.x; x < n * 32; x += blockDim.x) {
-      const int c = x >> 5, jj = blockIdx.x * 32 + (x & 31);
-      float sum = 0.f;
-      for (int w = 0; w < nwarp; ++w) sum += part[(w * SCAN_CT + c) * 32 + (x & 31)];
-      if (jj < Dv) out[((long)(c0 + c) * H + h) * Dv + jj] = sum;
+    for (; c < n; ++c) {
+      float acc = update(c);
+#pragma unroll
+      for (int o = 1; o < RGP2; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (rg == 0) os[c][col] = acc;
     }
+    __syncthreads();  // the chunk's outputs are complete; nobody reads this half of the buffers any more
+    for (int x = tid; x < n * SCAN_VT; x += THREADS) {
+      const int c = x / SCAN_VT, jj = blockIdx.x * SCAN_VT + (x % SCAN_VT);
+      if (jj < Dv) out[((long)(c0 + c) * H + h) * Dv + jj] = os[c][x % SCAN_VT];
+    }
+    if (more) stage(c0 + SCAN_CT, buf ^ 1);
     __syncthreads();
   }
 #pragma unroll
   for (int r = 0; r < SCAN_R; ++r) {
-    const int i = warp * SCAN_R + r;
+    const int i = rg * SCAN_R + r;
     if (i < D && j < Dv) Sg[(long)i * Dv + j] = S[r];
   }
+}
+
+template <typename T, int RGP2, int SCAN_R, int SCAN_VT>
+static cudaError_t launch_scan(cudaStream_t stream, int num_seqs, const void* q, long q_stride, const void* k,
+                               long k_stride, const void* v, long v_stride, const void* z, long z_stride,
+                               const float* z_bias, float inv_tau, const float* head_decay, const float* inv_freq,
+                               int rot_pairs, const int* positions, float q_scale, float k_scale, float* state,
+                               const int* cu_seqlens, const int* state_slots, float* out, int H, int D, int Dv) {
+  constexpr size_t smem = (size_t)(6 * SCAN_CT * RGP2 * SCAN_R + 3 * SCAN_CT * SCAN_VT) * sizeof(float);
+  auto kernel = decayed_state_scan_kernel<T, RGP2, SCAN_R, SCAN_VT>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const dim3 grid((Dv + SCAN_VT - 1) / SCAN_VT, H, num_seqs);
+  return launch_pdl(kernel, grid, dim3(SCAN_VT * RGP2), smem, stream, (const T*)q, q_stride,
+                    (const T*)k, k_stride, (const T*)v, v_stride, (const T*)z, z_stride, z_bias, inv_tau, head_decay,
+                    inv_freq, rot_pairs, positions, q_scale, k_scale, state, cu_seqlens, state_slots, out, H, D, Dv);
 }
 
 // q, k: head h of token t at [t * stride + h * D]; v at [t * v_stride + h * Dv]; z (decay logits, or
@@ -143,30 +225,19 @@ Q3_EXPORT int q3_decayed_state_scan(int dtype, const void* q, long q_stride, con
   if (!z && !head_decay) return Q3_ERR_ARGUMENT;
   if (rot_pairs < 0 || 2 * rot_pairs > D || (rot_pairs && (!inv_freq || !positions))) return Q3_ERR_ARGUMENT;
   if (H < 1 || D < 1 || Dv < 1 || H > 65535 || num_seqs > 65535) return Q3_ERR_ARGUMENT;
-  if (D > 32 * SCAN_R) return Q3_ERR_UNSUPPORTED;
+  if (D > 256 || (dtype != Q3_DTYPE_F32 && dtype != Q3_DTYPE_BF16)) return Q3_ERR_UNSUPPORTED;
   if (num_seqs == 0) return Q3_OK;
-  const int nwarp = (D + SCAN_R - 1) / SCAN_R;
-  const int Dp = nwarp * SCAN_R;
-  const size_t smem = (size_t)(3 * SCAN_CT * Dp + SCAN_CT * 32 + nwarp * SCAN_CT * 32) * sizeof(float);
-  const dim3 grid((Dv + 31) / 32, H, num_seqs);
   cudaError_t e;
-  if (dtype == Q3_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(decayed_state_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_pdl(decayed_state_scan_kernel<float>, grid, dim3(32 * nwarp), smem, stream, (const float*)q, q_stride,
-                   (const float*)k, k_stride, (const float*)v, v_stride, (const float*)z, z_stride, z_bias, inv_tau,
-                   head_decay, inv_freq, rot_pairs, positions, q_scale, k_scale, state, cu_seqlens, state_slots, out, H,
-                   D, Dv);
-  } else if (dtype == Q3_DTYPE_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(decayed_state_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_pdl(decayed_state_scan_kernel<bf16>, grid, dim3(32 * nwarp), smem, stream, (const bf16*)q, q_stride,
-                   (const bf16*)k, k_stride, (const bf16*)v, v_stride, (const bf16*)z, z_stride, z_bias, inv_tau,
-                   head_decay, inv_freq, rot_pairs, positions, q_scale, k_scale, state, cu_seqlens, state_slots, out, H,
-                   D, Dv);
-  } else {
-    return Q3_ERR_ARGUMENT;
-  }
+#define Q3_SCAN(T, RGP2, R, VT)                                                                                      \
+  e = launch_scan<T, RGP2, R, VT>(stream, num_seqs, q, q_stride, k, k_stride, v, v_stride, z, z_stride, z_bias,      \
+                                  inv_tau, head_decay, inv_freq, rot_pairs, positions, q_scale, k_scale, state,      \
+                                  cu_seqlens, state_slots, out, H, D, Dv)
+#define Q3_SCAN_SIZES(T)                                                                                             \
+  if (D <= 16) Q3_SCAN(T, 4, 4, 16); else if (D <= 32) Q3_SCAN(T, 8, 4, 16); else if (D <= 64) Q3_SCAN(T, 16, 4, 16); \
+  else if (D <= 128) Q3_SCAN(T, 32, 4, 16); else Q3_SCAN(T, 32, 8, 32)
+  if (dtype == Q3_DTYPE_F32) { Q3_SCAN_SIZES(float); } else { Q3_SCAN_SIZES(bf16); }
+#undef Q3_SCAN_SIZES
+#undef Q3_SCAN
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 

@@ -490,6 +490,27 @@ __global__ void relu_squared_kernel(const T* __restrict__ x, long x_stride, T* _
   out[idx] = from_f32<T>(v * v);
 }
 
+// The same with 16-byte accesses: n and x_stride multiples of 8, both pointers 16-byte aligned.
+template <typename T>
+__global__ void relu_squared_vec_kernel(const T* __restrict__ x, long x_stride, T* __restrict__ out, long chunks,
+                                        int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= chunks) return;
+  const int per_row = n / 8;
+  const long t = idx / per_row;
+  const int i = (int)(idx - t * per_row) * 8;
+  float v[8];
+  load8(x + t * x_stride + i, v);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float r = fmaxf(v[e], 0.f);
+    v[e] = r * r;
+  }
+  store8(out + t * n + i, v);
+}
+
 Q3_EXPORT int q3_relu_squared(int dtype, const void* x, long x_stride, void* out, int num_rows, int n,
                               cudaStream_t stream) {
   if (!x || !out || n < 1 || x_stride < n) return Q3_ERR_ARGUMENT;
@@ -497,6 +518,18 @@ Q3_EXPORT int q3_relu_squared(int dtype, const void* x, long x_stride, void* out
   if (total == 0) return Q3_OK;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaError_t e;
+  if (n % 8 == 0 && x_stride % 8 == 0 && aligned16(x) && aligned16(out) &&
+      (dtype == Q3_DTYPE_F32 || dtype == Q3_DTYPE_BF16)) {
+    const long chunks = total / 8;
+    const unsigned vblocks = (unsigned)((chunks + 255) / 256);
+    if (dtype == Q3_DTYPE_F32)
+      e = launch_pdl(relu_squared_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (const float*)x, x_stride,
+                     (float*)out, chunks, n);
+    else
+      e = launch_pdl(relu_squared_vec_kernel<bf16>, dim3(vblocks), dim3(256), 0, stream, (const bf16*)x, x_stride,
+                     (bf16*)out, chunks, n);
+    return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
+  }
   if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, x_stride,
                    (float*)out, total, n);

@@ -9,7 +9,9 @@
 // the last one stopped; conv_state_update writes them after conv_rope_store has read the old ones.
 // The convolution accumulates in fp32 in tap order; its result is rotated in fp32 and rounded once.
 //
-// conv_rope_store: one block per token.  The token's C results are kept in shared memory, then
+// conv_rope_store: one thread per (token, work item); a work item is a rotation pair (i, i + pairs) of
+// a q or k head, an element of such a head that does not turn, or an element of a v head, so that no
+// thread waits for another and every thread's few loads are in flight at once.
 //   q heads: pairs (i, i + pairs) of a head turn by position * inv_freq[i], written to q_out
 //   k heads: the same, written to the token's row of k_pages
 //   v heads: multiplied by value_scale, written to the token's row of v_pages
@@ -17,6 +19,21 @@
 #include "common.cuh"
 
 #define CONV_MAX_TAPS 16
+
+// One channel's convolution at the token that is `n` rows into its sequence's portion.
+template <typename T>
+__device__ __forceinline__ float conv_channel(const T* __restrict__ xrow, long x_stride, const float* __restrict__ w,
+                                              int taps, const float* __restrict__ srow, int C, int n, int c) {
+  if (taps <= 0) return to_f32(xrow[c]);
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int back = taps - 1 - j;  // how many tokens before this one
+    const float u = n - back >= 0 ? to_f32(xrow[-(long)back * x_stride + c])
+                                  : srow[(long)(taps - 1 + n - back) * C + c];
+    acc = fmaf(w[(long)j * C + c], u, acc);
+  }
+  return acc;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -27,60 +44,52 @@ conv_rope_store_kernel(const T* __restrict__ x, long x_stride, const float* __re
                        T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                        const int* __restrict__ block_table, int max_pages, int ps, int nq, int nkv, int D, int Dv,
                        float value_scale, int write_kv) {
-  extern __shared__ float ys[];  // C
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  const int per_head = D - rot_pairs;  // work items of a q or k head: its pairs, then what does not turn
+  const int qk_items = (nq + nkv) * per_head;
+  if (item >= qk_items + nkv * Dv) return;
   const int b = token_seq[t];
   const int p = positions[t];
   const int Cq = nq * D, Ck = nkv * D, C = Cq + Ck + nkv * Dv;
   const int n = t - cu_seqlens[b];  // the token's place in its sequence's portion
   const T* xrow = x + (long)t * x_stride;
-  if (taps > 0) {
-    const float* srow = conv_state + (long)state_slots[b] * (taps - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int back = taps - 1 - j;  // how many tokens before this one
-        const float u = n - back >= 0 ? to_f32(xrow[-(long)back * x_stride + c])
-                                      : srow[(long)(taps - 1 + n - back) * C + c];
-        acc = fmaf(w[(long)c * taps + j], u, acc);
-      }
-      ys[c] = acc;
-    }
+  const float* srow = taps > 1 ? conv_state + (long)state_slots[b] * (taps - 1) * C : nullptr;
+  if (item >= qk_items) {  // an element of a v head
+    if (!write_kv) return;
+    const int c = item - qk_items, head = c / Dv, e = c - head * Dv;
+    const int page = block_table[(long)b * max_pages + p / ps];
+    const float y = conv_channel(xrow, x_stride, w, taps, srow, C, n, Cq + Ck + c);
+    v_pages[(((long)page * nkv + head) * ps + p % ps) * Dv + e] = from_f32<T>(y * value_scale);
+    return;
+  }
+  const int head = item / per_head, r = item - head * per_head;  // q heads, then k heads
+  const bool is_q = head < nq;
+  if (!is_q && !write_kv) return;
+  T* dst;
+  if (is_q) {
+    dst = q_out + (long)t * Cq + (long)head * D;
   } else {
-    for (int c = threadIdx.x; c < C; c += blockDim.x) ys[c] = to_f32(xrow[c]);
+    const int page = block_table[(long)b * max_pages + p / ps];
+    dst = k_pages + (((long)page * nkv + (head - nq)) * ps + p % ps) * D;
   }
-  __syncthreads();
-  const int page = write_kv ? block_table[(long)b * max_pages + p / ps] : 0;
-  const int dims = 2 * rot_pairs;
-  // q and k heads: an element of the first half of the rotated part writes both elements of its pair
-  for (int c = threadIdx.x; c < Cq + Ck; c += blockDim.x) {
-    const bool is_q = c < Cq;
-    if (!is_q && !write_kv) continue;
-    const int hc = is_q ? c : c - Cq;
-    const int head = hc / D, e = hc - head * D;
-    T* dst = is_q ? q_out + (long)t * Cq + hc
-                  : k_pages + ((((long)page * nkv + head) * ps + p % ps) * D + e);
-    if (e >= dims) {
-      *dst = from_f32<T>(ys[c]);
-    } else if (e < rot_pairs) {
-      float sn, cs;
-      sincosf((float)p * inv_freq[e], &sn, &cs);
-      const float u = ys[c], v = ys[c + rot_pairs];
-      dst[0] = from_f32<T>(u * cs - v * sn);
-      dst[rot_pairs] = from_f32<T>(v * cs + u * sn);
-    }
+  if (r >= rot_pairs) {  // beyond the rotated part
+    const int e = r + rot_pairs;
+    dst[e] = from_f32<T>(conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + e));
+    return;
   }
-  if (write_kv)
-    for (int c = threadIdx.x; c < nkv * Dv; c += blockDim.x) {
-      const int head = c / Dv, e = c - head * Dv;
-      v_pages[(((long)page * nkv + head) * ps + p % ps) * Dv + e] = from_f32<T>(ys[Cq + Ck + c] * value_scale);
-    }
+  const float u = conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + r);
+  const float v = conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + r + rot_pairs);
+  float sn, cs;
+  sincosf((float)p * inv_freq[r], &sn, &cs);
+  dst[r] = from_f32<T>(u * cs - v * sn);
+  dst[r + rot_pairs] = from_f32<T>(v * cs + u * sn);
 }
 
 // x: [T, C] rows x_stride apart, C = nq * D + nkv * D + nkv * Dv (q heads, k heads, v heads); w: fp32
-// [C, taps] (taps = 0: no convolution, conv_state unused); conv_state: fp32 [slots, taps - 1, C];
+// [taps, C], tap-major so that neighbouring channels' weights are neighbours (taps = 0: no convolution, conv_state unused); conv_state: fp32 [slots, taps - 1, C];
 // inv_freq: fp32 [rot_pairs] or rot_pairs = 0; q_out: dense [T, nq * D]; k_pages [pages, nkv, ps, D],
 // v_pages [pages, nkv, ps, Dv].
 Q3_EXPORT int q3_conv_rope_store(int dtype, const void* x, long x_stride, const float* w, int taps,
@@ -96,20 +105,17 @@ Q3_EXPORT int q3_conv_rope_store(int dtype, const void* x, long x_stride, const 
   if (nq < 1 || nkv < 1 || D < 1 || Dv < 1 || rot_pairs < 0 || 2 * rot_pairs > D || (rot_pairs && !inv_freq))
     return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
-  const size_t smem = (size_t)(nq * D + nkv * D + nkv * Dv) * sizeof(float);
-  if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
+  const int items = (nq + nkv) * (D - rot_pairs) + nkv * Dv;
+  if ((items + 255) / 256 > 65535) return Q3_ERR_UNSUPPORTED;
+  const dim3 grid(num_tokens, (items + 255) / 256);
   cudaError_t e;
   if (dtype == Q3_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(conv_rope_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_pdl(conv_rope_store_kernel<float>, dim3(num_tokens), dim3(256), smem, stream, (const float*)x, x_stride,
+    e = launch_pdl(conv_rope_store_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, x_stride,
                    w, taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs,
                    (float*)q_out, (float*)k_pages, (float*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv,
                    value_scale, write_kv);
   } else if (dtype == Q3_DTYPE_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(conv_rope_store_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_pdl(conv_rope_store_kernel<bf16>, dim3(num_tokens), dim3(256), smem, stream, (const bf16*)x, x_stride, w,
+    e = launch_pdl(conv_rope_store_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, x_stride, w,
                    taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs, (bf16*)q_out,
                    (bf16*)k_pages, (bf16*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv, value_scale, write_kv);
   } else {

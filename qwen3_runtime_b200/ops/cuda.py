@@ -465,18 +465,18 @@ class CudaOps:
                         positions, token_seq, cu_seqlens, state_slots, num_seqs, block_table, k_pages, v_pages,
                         page_size, q_out, value_scale=1.0, write_kv=True):
         """Short causal convolution on every channel of ``x`` ``[T, q heads | k heads | v heads]``
-        (``conv_weight`` float32 ``[C, taps]`` or None; the rows before a step's first token come from
+        (``conv_weight`` float32 ``[taps, C]``, tap-major, or None; the rows before a step's first token come from
         ``conv_state`` float32 ``[slots, taps - 1, C]``, which is brought up to date afterwards), rotation
         of q and k (pair i = elements i and i + pairs, angle ``position * inv_freq[i]``), q into
         ``q_out``, k and ``value_scale * v`` into the token's page row (csrc/short_conv.cu)."""
         T = x.shape[0]
         C = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
-        taps = conv_weight.shape[1] if conv_weight is not None else 0
+        taps = conv_weight.shape[0] if conv_weight is not None else 0
         if x.stride(1) != 1 or x.shape[1] != C or not q_out.is_contiguous():
             raise KernelError("conv_rope_store: rows of q, k and v heads; a dense q output")
         if taps and (conv_weight.dtype != torch.float32 or not conv_weight.is_contiguous()
-                     or conv_weight.shape[0] != C):
-            raise KernelError("conv_rope_store: a dense float32 weight [channels, taps]")
+                     or conv_weight.shape[1] != C):
+            raise KernelError("conv_rope_store: a dense float32 weight [taps, channels]")
         if taps > 1 and (conv_state.dtype != torch.float32 or not conv_state.is_contiguous()
                          or conv_state.shape[1:] != (taps - 1, C)):
             raise KernelError("conv_rope_store: the state is dense float32 [slots, taps - 1, channels]")
@@ -1010,6 +1010,8 @@ class CudaOps:
     @staticmethod
     def _library_mm(x, weight, out, out_dtype):
         if out_dtype is not None and out_dtype != x.dtype:
+            if out is not None:
+                return torch.mm(x, weight.t(), out_dtype=out_dtype, out=out)
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         if out is None:
             return torch.mm(x, weight.t())

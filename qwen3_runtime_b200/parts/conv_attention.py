@@ -60,7 +60,8 @@ class ConvWindowAttention(BranchMixer):
         self.in_weight = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0).contiguous()
         self.o_weight = tensors["o"].contiguous()
         if self.taps:
-            self.conv_weight = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
+            # tap-major [taps, channels]: the kernel's neighbouring channels read neighbouring weights
+            self.conv_weight = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).t().contiguous()
 
     def input_weight(self):
         return self.in_weight
@@ -77,7 +78,23 @@ class ConvWindowAttention(BranchMixer):
     def kernel_groups(self):
         groups = ["short_conv", "attention_generic"]
         groups += ["gemm_f32"] if self.ctx.dtype == torch.float32 else ["gemm_small_m", "gemm_stream"]
+        if self._specialised():
+            groups += ["attention_decode", "attention_prefill"]
         return groups
+
+    def _specialised(self) -> bool:
+        """Keys and values of one size that the split-KV decode kernel and the tensor-core prompt kernel
+        take (ops.paged_attention sends a dense output there)."""
+        return (self.ctx.dtype == torch.bfloat16 and self.dim == self.vdim and self.dim in (64, 128)
+                and self.num_heads // self.num_kv_heads <= 16)
+
+    def step_choosers(self):
+        """Into how many slices the split-KV decode kernel cuts the longest sequence's keys."""
+        model = getattr(self.ops, "decode_slices_for", None)
+        if model is None or not self._specialised():
+            return {}
+        nkv, D, window = self.num_kv_heads, self.dim, self.window
+        return {("decode_slices", nkv, D, window): lambda kv_lens: model(kv_lens, nkv, D, window)}
 
     def cache_spec(self):
         pages = KVLayerSpec(self.num_kv_heads, self.dim, self.window, value_dim=self.vdim)
@@ -105,7 +122,8 @@ class ConvWindowAttention(BranchMixer):
         ops.paged_attention(q, q.stride(0), num_heads=H, num_kv_heads=G, head_dim=D, k_pages=pages.k_pages,
                             v_pages=pages.v_pages, block_table=block_table, token_seq=step.token_seq,
                             positions=step.positions, out=out, page_size=pages.page_size, scale=self.scale,
-                            window=self.window, step=step, value_dim=Dv)
+                            window=self.window, step=step, value_dim=Dv,
+                            decode_slices=step.choices.get(("decode_slices", G, D, self.window)))
 
 
 register_part("mixer", "conv_window_attention", ConvWindowAttention)

@@ -198,9 +198,12 @@ class Retention(_DecayedStateMixer):
 
 class ParallelMixer(Part):
     """Several mixers side by side on the same input; the result is the sum of their outputs, each
-    times its own scale.  The branches' input matrices are one product and so are their output
-    projections: every branch writes ``scale * (what its output projection reads)`` into its columns
-    of one buffer, and the projections, laid side by side, multiply that buffer once.
+    times its own scale.  The branches' input matrices are one product.  Every branch writes
+    ``scale * (what its output projection reads)``; where the norm that takes the mixer's output adds
+    partial sums, each branch's output projection is a product of its own into one float32 plane and
+    the norm adds the planes (no kernel adds the branches up, and every branch has a dense buffer,
+    which the specialised attention kernels want); else the branches write into their columns of one
+    buffer and the projections, laid side by side, multiply that buffer once.
     ``branches``: ``[(prefix, PartSpec of a BranchMixer, scale), ...]``."""
 
     category = "mixer"
@@ -225,7 +228,7 @@ class ParallelMixer(Part):
         for prefix, part, _ in self.branches:
             part.load({name: tensors[prefix + name] for name in part.param_specs()})
         self.in_weight, self.in_starts = _pad_rows([part.input_weight() for _, part, _ in self.branches])
-        self.o_weight = torch.cat([part.output_weight() for _, part, _ in self.branches], dim=1).contiguous()
+        self.o_weight = None  # the projections side by side; made when first needed
         self.in_sizes = [part.input_weight().shape[0] for _, part, _ in self.branches]
         at = 0
         for _, part, _ in self.branches:
@@ -248,10 +251,20 @@ class ParallelMixer(Part):
 
     def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
         proj = self.ops.linear(h, self.in_weight)
-        ctx = torch.empty((h.shape[0], self.o_weight.shape[1]), dtype=h.dtype, device=h.device)
+        T = h.shape[0]
+        if self.partial_sums_ok:
+            planes = torch.empty((len(self.branches), T, self.in_weight.shape[1]), dtype=torch.float32, device=h.device)
+            for i, ((_, part, scale), a, n, view) in enumerate(zip(self.branches, self.in_starts, self.in_sizes, cache)):
+                ctx = torch.empty((T, part.context_size()), dtype=h.dtype, device=h.device)
+                part.context(proj[:, a:a + n], step, view, ctx, scale)
+                self.ops.linear(ctx, part.output_weight(), out=planes[i], out_dtype=torch.float32)
+            return planes
+        if self.o_weight is None:
+            self.o_weight = torch.cat([part.output_weight() for _, part, _ in self.branches], dim=1).contiguous()
+        ctx = torch.empty((T, self.o_weight.shape[1]), dtype=h.dtype, device=h.device)
         for (_, part, scale), a, n, b, view in zip(self.branches, self.in_starts, self.in_sizes, self.out_starts, cache):
             part.context(proj[:, a:a + n], step, view, ctx[:, b:b + part.context_size()], scale)
-        return self.ops.linear(ctx, self.o_weight, partial_sums=self.partial_sums_ok)
+        return self.ops.linear(ctx, self.o_weight)
 
 
 register_part("mixer", "gla", GatedLinearAttention)

@@ -120,7 +120,7 @@ class TorchOps:
         nq, nkv, D, Dv = num_heads, num_kv_heads, head_dim, value_dim
         u = x.float()
         y = u.clone()
-        taps = conv_weight.shape[1] if conv_weight is not None else 0
+        taps = conv_weight.shape[0] if conv_weight is not None else 0  # [taps, C]
         if taps:
             for b in range(num_seqs):
                 t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
@@ -130,7 +130,7 @@ class TorchOps:
                 for n in range(t1 - t0):
                     acc = u.new_zeros(C)
                     for j in range(taps):
-                        acc = acc + conv_weight[:, j].float() * rows[n + j]
+                        acc = acc + conv_weight[j].float() * rows[n + j]
                     y[t0 + n] = acc
                 if taps > 1:
                     conv_state[slot] = rows[rows.shape[0] - (taps - 1):]

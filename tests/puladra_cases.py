@@ -75,6 +75,17 @@ CONFIGS = {
                                                                  rot=RotationConfig(4, 50.0))),
                                    MoeConfig(2, 1, 32, 32)),
                 PuladraLayerConfig("gla", _gla(heads=2, dim=16, vdim=24, tau=8.0, decay_rank=8), None)))),
+    # keys and values of one size (64) in groups of four query heads: in bfloat16 the specialised attention
+    # kernels (split-KV decode, tensor-core prompt portions) take the windowed branch
+    "X": dict(page_size=16, seed=34, config=PuladraConfig(
+        vocab=210, width=128, norm_eps=1e-5, logit_scale=1.2, side_dim=16, loop_start=0, loop_stop=1, loop_times=2,
+        layers=(PuladraLayerConfig("parallel", _par(left=_left(heads=8, kv_heads=2, dim=64, vdim=64, conv=3, window=40,
+                                                               rot=RotationConfig(64, 10000.0), scale=0.125),
+                                                    right=_right(heads=2, dim=32, vdim=64, decay=(0.97, 0.999),
+                                                                 rot=RotationConfig(32, 1e5))),
+                                   MoeConfig(4, 2, 64, 32)),
+                PuladraLayerConfig("gla", _gla(heads=2, dim=64, vdim=128, tau=16.0, decay_rank=16),
+                                   MoeConfig(8, 3, 32, 0))))),
 }
 
 STD = 0.15  # spread of the random matrices: attention, states and experts have to matter
@@ -94,7 +105,7 @@ def _every_expert(cfg: PuladraConfig) -> PuladraConfig:
     return dataclasses.replace(cfg, layers=layers)
 
 
-for _name in ("U", "V", "W"):
+for _name in ("U", "V", "W", "X"):
     CONFIGS[_name + "all"] = dict(CONFIGS[_name], config=_every_expert(CONFIGS[_name]["config"]))
 
 
@@ -527,7 +538,7 @@ def case_convolution_across_portions(dtype, ops, device, *, taps=4, heads=2, kv_
         x = torch.stack([u[b, t] for b, t in rows]).to(device=device, dtype=dt)
         q_out = torch.empty((len(rows), heads * D), dtype=dt, device=device)
         ops.conv_rope_store(x, num_heads=heads, num_kv_heads=kv_heads, head_dim=D, value_dim=Dv,
-                            conv_weight=w.to(device), conv_state=state, inv_freq=inv.to(device),
+                            conv_weight=w.t().contiguous().to(device), conv_state=state, inv_freq=inv.to(device),
                             positions=step.positions, token_seq=step.token_seq, cu_seqlens=step.cu_seqlens,
                             state_slots=step.state_slots, num_seqs=2, block_table=step.block_tables[0],
                             k_pages=k_pages, v_pages=v_pages, page_size=page_size, q_out=q_out, value_scale=0.5)

@@ -98,12 +98,12 @@ def test_stream_extras(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["U", "V", "W"])
+@pytest.mark.parametrize("name", ["U", "V", "W", "X"])
 def test_schedules(tmp_path, ops, name, dtype):
     pc.case_schedules(tmp_path, name, dtype, ops, DEV)
 
 
-@pytest.mark.parametrize("name", ["U", "V"])
+@pytest.mark.parametrize("name", ["U", "V", "X"])
 def test_schedules_through_captured_decode_steps(tmp_path, ops, name):
     pc.case_schedules(tmp_path, name, "bfloat16", ops, DEV, cuda_graph=True)
     pc.case_schedules(tmp_path, name, "float32", ops, DEV, cuda_graph=True, lengths=(40, 5, 33))
@@ -113,6 +113,7 @@ def test_schedules_through_captured_decode_steps(tmp_path, ops, name):
 def test_long_decode(tmp_path, ops, dtype):
     pc.case_long_decode(tmp_path, "U", dtype, ops, DEV, total=200, cuda_graph=True)
     pc.case_long_decode(tmp_path, "V", dtype, ops, DEV, total=120)
+    pc.case_long_decode(tmp_path, "X", dtype, ops, DEV, total=120, cuda_graph=True)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
