@@ -2,15 +2,18 @@
 // device, the experts' two products over their own slots, and the per-token sum.
 //
 //   route_top      z = W_router h in fp32, the `top` largest z (the order of their sigmoids; lowest
-//                  index on a tie) with sigmoid(z) as weights (optionally divided by their sum)
+//                  index on a tie) with sigmoid(z) as weights (optionally divided by their sum), or
+//                  with the softmax over the chosen z as weights
 //   group_slots    slots sorted by expert: offsets[E + 1], order[S], and for the products the
 //                  first row tile of each expert, tile_offsets[E + 1] (tiles of `bm` slots)
 //   expert_gate_up mid[slot] = glu(W_gate_e x, W_up_e x), x = h[token] * weight (rounded to the
 //                  operand type) when the weight multiplies the expert's input
 //                  glu: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + off)
+//   expert_up      mid[slot] = relu(W_up_e h[token])^2: the first product of an expert without a gate
 //   expert_down    y[slot] = W_down_e mid[slot]
 //   combine        out[t] = sum over the token's slots of y (times the weight when it multiplies
-//                  the output), plus the shared expert's result, summed in fp32 in slot order
+//                  the output), plus the shared expert's result (times the sigmoid of a gate logit, if
+//                  one is given), summed in fp32 in slot order
 //
 // Products accumulate in fp32 on the FMA pipes, each output one accumulator over ascending k, so a
 // token's result does not depend on which other tokens chose the same expert.  Nothing here reads

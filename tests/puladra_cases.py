@@ -86,6 +86,21 @@ CONFIGS = {
                                    MoeConfig(4, 2, 64, 32)),
                 PuladraLayerConfig("gla", _gla(heads=2, dim=64, vdim=128, tau=16.0, decay_rank=16),
                                    MoeConfig(8, 3, 32, 0))))),
+    # no layer with pages at all, a loop of a single pass over the last layer, more experts than a warp's
+    # worth of lanes would suggest (9, five chosen)
+    "Y": dict(page_size=16, seed=35, config=PuladraConfig(
+        vocab=64, width=40, norm_eps=1e-5, logit_scale=1.0, side_dim=0, loop_start=1, loop_stop=2, loop_times=1,
+        layers=(PuladraLayerConfig("gla", _gla(heads=2, dim=16, vdim=24, tau=8.0, decay_rank=8), MoeConfig(9, 5, 16, 0)),
+                PuladraLayerConfig("gla", _gla(heads=2, dim=16, vdim=24, tau=8.0, decay_rank=8), None)))),
+    # every layer parallel, a convolution of one tap (nothing is carried), a rotation of one pair, as many
+    # key/value heads as query heads, a window shorter than a page
+    "Z": dict(page_size=16, seed=36, config=PuladraConfig(
+        vocab=64, width=40, norm_eps=1e-5, logit_scale=2.0, side_dim=3, layers=(
+            PuladraLayerConfig("parallel", _par(left=_left(conv=1, heads=4, kv_heads=4, dim=8, vdim=8,
+                                                           rot=RotationConfig(2, 10.0), window=5)), None),
+            PuladraLayerConfig("parallel", _par(left=_left(conv=1, heads=4, kv_heads=4, dim=8, vdim=8,
+                                                           rot=RotationConfig(2, 10.0), window=5)),
+                               MoeConfig(9, 5, 16, 0))))),
 }
 
 STD = 0.15  # spread of the random matrices: attention, states and experts have to matter
@@ -105,7 +120,7 @@ def _every_expert(cfg: PuladraConfig) -> PuladraConfig:
     return dataclasses.replace(cfg, layers=layers)
 
 
-for _name in ("U", "V", "W", "X"):
+for _name in ("U", "V", "W", "X", "Y", "Z"):
     CONFIGS[_name + "all"] = dict(CONFIGS[_name], config=_every_expert(CONFIGS[_name]["config"]))
 
 

@@ -55,7 +55,7 @@ def test_cache_layers_of_a_parallel_mixer(tmp_path):
     assert conv is None and pages.window is None
 
 
-@pytest.mark.parametrize("name", ["U", "V", "W", "X"])
+@pytest.mark.parametrize("name", ["U", "V", "W", "X", "Y", "Z"])
 def test_schedules(tmp_path, name):
     pc.case_schedules(tmp_path, name, "float32", OPS, DEV)
 

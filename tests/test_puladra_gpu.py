@@ -98,12 +98,12 @@ def test_stream_extras(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["U", "V", "W", "X"])
+@pytest.mark.parametrize("name", ["U", "V", "W", "X", "Y", "Z"])
 def test_schedules(tmp_path, ops, name, dtype):
     pc.case_schedules(tmp_path, name, dtype, ops, DEV)
 
 
-@pytest.mark.parametrize("name", ["U", "V", "X"])
+@pytest.mark.parametrize("name", ["U", "V", "X", "Y"])
 def test_schedules_through_captured_decode_steps(tmp_path, ops, name):
     pc.case_schedules(tmp_path, name, "bfloat16", ops, DEV, cuda_graph=True)
     pc.case_schedules(tmp_path, name, "float32", ops, DEV, cuda_graph=True, lengths=(40, 5, 33))
