@@ -266,6 +266,45 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   }
 }
 
+// The same with 16-byte accesses for value sizes up to 256 that are multiples of 8 (rows 16-byte
+// aligned): a lane keeps its eight values in registers between the sum of squares and the store, and a
+// warp takes as many (token, head) items as fit (`lph` lanes per item, a power of two >= Dv / 8).
+template <typename T>
+__global__ void head_norm_gate_vec_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                          const T* __restrict__ g, long g_stride, T* __restrict__ y, long y_stride,
+                                          float out_scale, long items, int H, int Dv, int lph) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, per_warp = 32 / lph;
+  const long item = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * per_warp + lane / lph;
+  const int d = (lane % lph) * 8;
+  const bool live = item < items && d < Dv;
+  const long t = live ? item / H : 0;
+  const int h = live ? (int)(item - t * H) : 0;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, gate[8];
+  float ss = 0.f;
+  if (live) {
+    load8(o + item * Dv + d, v);
+    load8(g + t * g_stride + (long)h * Dv + d, gate);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  for (int off = lph >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (!live) return;
+  const float rstd = rsqrtf(ss / (float)Dv + eps);
+  float wv[8];
+  if (w) load8(w + d, wv);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float val = v[e] * rstd;
+    if (w) val *= wv[e];
+    v[e] = val * (gate[e] / (1.f + expf(-gate[e]))) * out_scale;
+  }
+  store8(y + t * y_stride + (long)h * Dv + d, v);
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 // o: fp32 [T, H, Dv]; w: fp32 [Dv] shared by the heads, or null; g, y: head h of token t at
 // [t * stride + h * Dv].
 Q3_EXPORT int q3_head_norm_gate(int dtype, const float* o, const float* w, float eps, const void* g, long g_stride,
@@ -276,7 +315,19 @@ Q3_EXPORT int q3_head_norm_gate(int dtype, const float* o, const float* w, float
   if (items == 0) return Q3_OK;
   const unsigned blocks = (unsigned)((items + 7) / 8);
   cudaError_t e;
-  if (dtype == Q3_DTYPE_F32)
+  const bool vec = Dv % 8 == 0 && Dv <= 256 && g_stride % 8 == 0 && y_stride % 8 == 0 && aligned16(o) &&
+                   aligned16(g) && aligned16(y) && (!w || aligned16(w));
+  int lph = 1;  // lanes per (token, head) item
+  while (lph * 8 < Dv) lph <<= 1;
+  const long per_block = 8 * (32 / (lph > 32 ? 32 : lph));
+  const unsigned vblocks = (unsigned)((items + per_block - 1) / per_block);
+  if (vec && dtype == Q3_DTYPE_F32)
+    e = launch_pdl(head_norm_gate_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, o, w, eps, (const float*)g,
+                   g_stride, (float*)y, y_stride, out_scale, items, H, Dv, lph);
+  else if (vec && dtype == Q3_DTYPE_BF16)
+    e = launch_pdl(head_norm_gate_vec_kernel<bf16>, dim3(vblocks), dim3(256), 0, stream, o, w, eps, (const bf16*)g,
+                   g_stride, (bf16*)y, y_stride, out_scale, items, H, Dv, lph);
+  else if (dtype == Q3_DTYPE_F32)
     e = launch_pdl(head_norm_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, w, eps, (const float*)g,
                    g_stride, (float*)y, y_stride, out_scale, items, H, Dv);
   else if (dtype == Q3_DTYPE_BF16)

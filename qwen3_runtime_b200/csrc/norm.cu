@@ -366,6 +366,110 @@ __global__ void fused_post_norm_kernel(const void* __restrict__ pending_any, int
   for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<T>((vs[i] * rstd) * w[i]);
 }
 
+// The same with 16-byte accesses: H a multiple of 8 and every row 16-byte aligned (plane strides
+// multiples of 4 elements).
+template <typename T>
+__global__ void fused_post_norm_vec_kernel(const void* __restrict__ pending_any, int parts, long part_stride,
+                                           const float* __restrict__ post_w, float post_eps,
+                                           float* __restrict__ resid, const int* __restrict__ ids,
+                                           const T* __restrict__ table, const int* __restrict__ add_ids,
+                                           const T* __restrict__ add_table, const float* __restrict__ add_vec,
+                                           const int* __restrict__ rows, const float* __restrict__ w,
+                                           T* __restrict__ out, int H, float eps, int write_resid, int vocab) {
+  extern __shared__ __align__(16) float vals[];  // y[H], v[H], 33 for the reductions
+  float* ys = vals;
+  float* vs = vals + H;
+  float* red = vals + 2 * H;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const long src = rows ? rows[r] : r;
+  float post_rstd = 1.f;
+  const bool pending = pending_any != nullptr;
+  if (pending) {
+    const T* prow = static_cast<const T*>(pending_any) + src * H;
+    const float* frow = static_cast<const float*>(pending_any) + src * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float y[8];
+      if (parts) {
+        load8(frow + i, y);
+        for (int p = 1; p < parts; ++p) {
+          float pv[8];
+          load8(frow + p * part_stride + i, pv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] += pv[e];
+        }
+      } else {
+        load8(prow + i, y);
+      }
+      store8(ys + i, y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += y[e] * y[e];
+    }
+    if (post_w) post_rstd = rsqrtf(block_sum(ss, red) / (float)H + post_eps);
+  }
+  const T* trow = nullptr;
+  if (ids) {
+    int id = ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    trow = table + (long)id * H;
+  }
+  const T* arow = nullptr;
+  if (add_ids) {
+    int id = add_ids[src];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    arow = add_table + (long)id * H;
+  }
+  float* rrow = resid ? resid + src * H : nullptr;
+  T* orow = out + (long)r * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8], x[8];
+    if (trow) load8(trow + i, v); else load8(rrow + i, v);
+    if (pending) {
+      load8(ys + i, x);
+      if (post_w) {
+        float pw[8];
+        load8(post_w + i, pw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += (x[e] * post_rstd) * pw[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += x[e];
+      }
+    }
+    if (arow) {
+      load8(arow + i, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += x[e];
+    }
+    if (add_vec) {
+      load8(add_vec + i, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += x[e];
+    }
+    if (write_resid) store8(rrow + i, v);
+    if (!w) {
+      store8(orow + i, v);  // the sum itself, rounded to the output's type
+      continue;
+    }
+    store8(vs + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+  }
+  if (!w) return;
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8], wv[8];
+    load8(vs + i, v);
+    load8(w + i, wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = (v[e] * rstd) * wv[e];
+    store8(orow + i, v);
+  }
+}
+
 template <typename T>
 static int launch_fused_post_norm(const void* pending, int parts, long part_stride, const float* post_w, float post_eps,
                                   float* resid,
@@ -377,6 +481,18 @@ static int launch_fused_post_norm(const void* pending, int parts, long part_stri
   if (smem > 200 * 1024) return Q3_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(fused_post_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (H % 8 == 0 && part_stride % 4 == 0 && aligned16(pending) && aligned16(post_w) && aligned16(resid) &&
+      aligned16(table) && aligned16(add_table) && aligned16(add_vec) && aligned16(w) && aligned16(out)) {
+    int vthreads = ((H / 8 + 31) / 32) * 32;  // eight elements a thread
+    vthreads = vthreads > 512 ? 512 : vthreads;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(fused_post_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_pdl(fused_post_norm_vec_kernel<T>, dim3(num_rows), dim3(vthreads), smem, stream, pending, parts,
+                      part_stride, post_w, post_eps, resid, ids, (const T*)table, add_ids, (const T*)add_table, add_vec,
+                      rows, w, (T*)out, H, eps, write_resid, vocab) == cudaSuccess
+               ? Q3_OK
+               : Q3_ERR_LAUNCH;
+  }
   int threads = ((H / 4 + 31) / 32) * 32;  // about four elements a thread: the row's loads are all in flight at once
   threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
   return launch_pdl(fused_post_norm_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, pending, parts, part_stride,
