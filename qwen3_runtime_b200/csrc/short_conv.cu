@@ -10,8 +10,8 @@
 // The convolution accumulates in fp32 in tap order; its result is rotated in fp32 and rounded once.
 //
 // conv_rope_store: one thread per (token, work item); a work item is a rotation pair (i, i + pairs) of
-// a q or k head, an element of such a head that does not turn, or an element of a v head, so that no
-// thread waits for another and every thread's few loads are in flight at once.
+// four q or k heads in a row, an element of such heads that does not turn, or an element of four v
+// heads, so that no thread waits for another and every thread's loads are in flight at once.
 //   q heads: pairs (i, i + pairs) of a head turn by position * inv_freq[i], written to q_out
 //   k heads: the same, written to the token's row of k_pages
 //   v heads: multiplied by value_scale, written to the token's row of v_pages
@@ -20,22 +20,46 @@
 
 #define CONV_MAX_TAPS 16
 
-// One channel's convolution at the token that is `n` rows into its sequence's portion.
-template <typename T>
+// One channel's convolution at token `t` of the step, which is `n` rows into its sequence's portion.
+// The step's own rows are read whether or not they belong to the sequence (never before row 0 of the
+// step), so that these loads wait for nothing; the few rows that come from the state replace them.
+// TAPS > 0: the tap count at compile time, the loop unrolled, so that all loads are in flight at once;
+// TAPS < 0: any count (`taps`).
+template <typename T, int TAPS>
 __device__ __forceinline__ float conv_channel(const T* __restrict__ xrow, long x_stride, const float* __restrict__ w,
-                                              int taps, const float* __restrict__ srow, int C, int n, int c) {
-  if (taps <= 0) return to_f32(xrow[c]);
+                                              int taps, const float* __restrict__ srow, int C, int t, int n, int c) {
+  if (TAPS == 0) return to_f32(xrow[c]);
+  if (TAPS > 0) {
+    float u[TAPS > 0 ? TAPS : 1], wj[TAPS > 0 ? TAPS : 1];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int back = TAPS - 1 - j;  // how many tokens before this one
+      u[j] = to_f32(xrow[-(long)min(back, t) * x_stride + c]);
+      wj[j] = w[(long)j * C + c];
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int back = TAPS - 1 - j;
+      if (n - back < 0) u[j] = srow[(long)(TAPS - 1 + n - back) * C + c];
+      acc = fmaf(wj[j], u[j], acc);
+    }
+    return acc;
+  }
   float acc = 0.f;
   for (int j = 0; j < taps; ++j) {
-    const int back = taps - 1 - j;  // how many tokens before this one
-    const float u = n - back >= 0 ? to_f32(xrow[-(long)back * x_stride + c])
-                                  : srow[(long)(taps - 1 + n - back) * C + c];
+    const int back = taps - 1 - j;
+    float u = to_f32(xrow[-(long)min(back, t) * x_stride + c]);
+    if (n - back < 0) u = srow[(long)(taps - 1 + n - back) * C + c];
     acc = fmaf(w[(long)j * C + c], u, acc);
   }
   return acc;
 }
 
-template <typename T>
+// A thread takes one work item of CONV_HG heads in a row: with four (steps of many tokens) the loads of
+// all of them are in flight together, their angle is worked out once, and the step's tokens pass in a
+// quarter of the blocks; with one (a few tokens) a thread's chain is shortest.
+template <typename T, int TAPS, int CONV_HG>
 __global__ void __launch_bounds__(256)
 conv_rope_store_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int taps,
                        const float* __restrict__ conv_state, const int* __restrict__ positions,
@@ -49,43 +73,58 @@ conv_rope_store_kernel(const T* __restrict__ x, long x_stride, const float* __re
   const int t = blockIdx.x;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
   const int per_head = D - rot_pairs;  // work items of a q or k head: its pairs, then what does not turn
-  const int qk_items = (nq + nkv) * per_head;
-  if (item >= qk_items + nkv * Dv) return;
+  const int qk_groups = (nq + nkv + CONV_HG - 1) / CONV_HG, v_groups = (nkv + CONV_HG - 1) / CONV_HG;
+  const int qk_items = qk_groups * per_head;
+  if (item >= qk_items + v_groups * Dv) return;
   const int b = token_seq[t];
   const int p = positions[t];
   const int Cq = nq * D, Ck = nkv * D, C = Cq + Ck + nkv * Dv;
   const int n = t - cu_seqlens[b];  // the token's place in its sequence's portion
   const T* xrow = x + (long)t * x_stride;
   const float* srow = taps > 1 ? conv_state + (long)state_slots[b] * (taps - 1) * C : nullptr;
-  if (item >= qk_items) {  // an element of a v head
+  const int page = write_kv ? block_table[(long)b * max_pages + p / ps] : 0;
+  const long page_row = (long)page * nkv * ps + p % ps;  // head 0's row of the token in its page
+  if (item >= qk_items) {  // element e of CONV_HG v heads
     if (!write_kv) return;
-    const int c = item - qk_items, head = c / Dv, e = c - head * Dv;
-    const int page = block_table[(long)b * max_pages + p / ps];
-    const float y = conv_channel(xrow, x_stride, w, taps, srow, C, n, Cq + Ck + c);
-    v_pages[(((long)page * nkv + head) * ps + p % ps) * Dv + e] = from_f32<T>(y * value_scale);
+    const int vi = item - qk_items, group = vi / Dv, e = vi - group * Dv;
+    float y[CONV_HG];
+#pragma unroll
+    for (int hh = 0; hh < CONV_HG; ++hh) {
+      const int head = group * CONV_HG + hh;
+      y[hh] = head < nkv ? conv_channel<T, TAPS>(xrow, x_stride, w, taps, srow, C, t, n, Cq + Ck + head * Dv + e) : 0.f;
+    }
+#pragma unroll
+    for (int hh = 0; hh < CONV_HG; ++hh) {
+      const int head = group * CONV_HG + hh;
+      if (head < nkv) v_pages[(page_row + (long)head * ps) * Dv + e] = from_f32<T>(y[hh] * value_scale);
+    }
     return;
   }
-  const int head = item / per_head, r = item - head * per_head;  // q heads, then k heads
-  const bool is_q = head < nq;
-  if (!is_q && !write_kv) return;
-  T* dst;
-  if (is_q) {
-    dst = q_out + (long)t * Cq + (long)head * D;
-  } else {
-    const int page = block_table[(long)b * max_pages + p / ps];
-    dst = k_pages + (((long)page * nkv + (head - nq)) * ps + p % ps) * D;
+  const int group = item / per_head, r = item - group * per_head;  // q heads, then k heads
+  const bool turns = r < rot_pairs;
+  const int e = turns ? r : r + rot_pairs;  // the element (the first of its pair, if it turns)
+  float u[CONV_HG], v[CONV_HG];
+#pragma unroll
+  for (int hh = 0; hh < CONV_HG; ++hh) {
+    const int head = group * CONV_HG + hh;
+    const bool live = head < nq + nkv && (head < nq || write_kv);
+    u[hh] = live ? conv_channel<T, TAPS>(xrow, x_stride, w, taps, srow, C, t, n, head * D + e) : 0.f;
+    v[hh] = live && turns ? conv_channel<T, TAPS>(xrow, x_stride, w, taps, srow, C, t, n, head * D + e + rot_pairs) : 0.f;
   }
-  if (r >= rot_pairs) {  // beyond the rotated part
-    const int e = r + rot_pairs;
-    dst[e] = from_f32<T>(conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + e));
-    return;
+  float sn = 0.f, cs = 1.f;
+  if (turns) sincosf((float)p * inv_freq[r], &sn, &cs);
+#pragma unroll
+  for (int hh = 0; hh < CONV_HG; ++hh) {
+    const int head = group * CONV_HG + hh;
+    if (head >= nq + nkv || (head >= nq && !write_kv)) continue;
+    T* dst = head < nq ? q_out + (long)t * Cq + (long)head * D : k_pages + (page_row + (long)(head - nq) * ps) * D;
+    if (turns) {
+      dst[e] = from_f32<T>(u[hh] * cs - v[hh] * sn);
+      dst[e + rot_pairs] = from_f32<T>(v[hh] * cs + u[hh] * sn);
+    } else {
+      dst[e] = from_f32<T>(u[hh]);
+    }
   }
-  const float u = conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + r);
-  const float v = conv_channel(xrow, x_stride, w, taps, srow, C, n, head * D + r + rot_pairs);
-  float sn, cs;
-  sincosf((float)p * inv_freq[r], &sn, &cs);
-  dst[r] = from_f32<T>(u * cs - v * sn);
-  dst[r + rot_pairs] = from_f32<T>(v * cs + u * sn);
 }
 
 // x: [T, C] rows x_stride apart, C = nq * D + nkv * D + nkv * Dv (q heads, k heads, v heads); w: fp32
@@ -105,22 +144,36 @@ Q3_EXPORT int q3_conv_rope_store(int dtype, const void* x, long x_stride, const 
   if (nq < 1 || nkv < 1 || D < 1 || Dv < 1 || rot_pairs < 0 || 2 * rot_pairs > D || (rot_pairs && !inv_freq))
     return Q3_ERR_ARGUMENT;
   if (num_tokens == 0) return Q3_OK;
-  const int items = (nq + nkv) * (D - rot_pairs) + nkv * Dv;
+  const int hg = num_tokens > 64 ? 4 : 1;  // heads per thread
+  const int items = ((nq + nkv + hg - 1) / hg) * (D - rot_pairs) + ((nkv + hg - 1) / hg) * Dv;
   if ((items + 255) / 256 > 65535) return Q3_ERR_UNSUPPORTED;
   const dim3 grid(num_tokens, (items + 255) / 256);
-  cudaError_t e;
+  cudaError_t e = cudaErrorInvalidValue;
+#define Q3_CONV_HG(T, TAPS, HG)                                                                                      \
+  e = launch_pdl(conv_rope_store_kernel<T, TAPS, HG>, grid, dim3(256), 0, stream, (const T*)x, x_stride, w, taps,    \
+                 conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs, (T*)q_out,          \
+                 (T*)k_pages, (T*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv, value_scale, write_kv)
+#define Q3_CONV(T, TAPS)                                                                                             \
+  if (hg == 4) Q3_CONV_HG(T, TAPS, 4); else Q3_CONV_HG(T, TAPS, 1)
+#define Q3_CONV_TAPS(T)                                                                                              \
+  switch (taps) {                                                                                                    \
+    case 0: Q3_CONV(T, 0); break;                                                                                    \
+    case 1: Q3_CONV(T, 1); break;                                                                                    \
+    case 2: Q3_CONV(T, 2); break;                                                                                    \
+    case 3: Q3_CONV(T, 3); break;                                                                                    \
+    case 4: Q3_CONV(T, 4); break;                                                                                    \
+    default: Q3_CONV(T, -1); break;                                                                                  \
+  }
   if (dtype == Q3_DTYPE_F32) {
-    e = launch_pdl(conv_rope_store_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, x_stride,
-                   w, taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs,
-                   (float*)q_out, (float*)k_pages, (float*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv,
-                   value_scale, write_kv);
+    Q3_CONV_TAPS(float)
   } else if (dtype == Q3_DTYPE_BF16) {
-    e = launch_pdl(conv_rope_store_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, x_stride, w,
-                   taps, conv_state, positions, token_seq, cu_seqlens, state_slots, inv_freq, rot_pairs, (bf16*)q_out,
-                   (bf16*)k_pages, (bf16*)v_pages, block_table, max_pages, ps, nq, nkv, D, Dv, value_scale, write_kv);
+    Q3_CONV_TAPS(bf16)
   } else {
     return Q3_ERR_ARGUMENT;
   }
+#undef Q3_CONV_TAPS
+#undef Q3_CONV
+#undef Q3_CONV_HG
   return e == cudaSuccess ? Q3_OK : Q3_ERR_LAUNCH;
 }
 
